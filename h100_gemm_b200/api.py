@@ -1,0 +1,273 @@
+"""ctypes binding of the C ABI in include/b200_gemm.h.
+
+The Python names mirror the reference's host interface: ``gemm`` is ``gpu_gemm(GemmParams)``
+(matmul_h100.cu.jinja:927-985), ``run_kernel`` is ``runKernel`` (matmul_h100_optimal.cu:32-59),
+``reference_gpu_gemm`` is the naive device GEMM of reference.h:78-90, and ``GemmConfig`` carries
+the template variables of matmul_h100.cu.jinja:9-14. Tensors are torch CUDA tensors used purely
+as device-memory handles; all arithmetic happens in the shared library's kernels.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Optional
+
+_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libb200gemm.so"
+_lib = None
+
+STATUS_OK = 0
+STATUS_INVALID_ARG = 1
+STATUS_UNSUPPORTED_CFG = 2
+STATUS_SMEM = 3
+STATUS_WORKSPACE = 4
+STATUS_CUDA = 5
+STATUS_DEVICE_TIMEOUT = 6
+
+
+class GemmError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"b200_gemm status {status}: {message}")
+        self.status = status
+
+
+class _Cfg(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in (
+        "block_m", "block_n", "block_k", "stages", "cluster_m", "cluster_n", "sched", "split_k",
+        "raster", "group", "c_col_major", "max_ctas")]
+
+
+@dataclass
+class GemmConfig:
+    """Tunable surface; field meanings are documented in include/b200_gemm.h."""
+    block_m: int = 128
+    block_n: int = 256
+    block_k: int = 64
+    stages: int = 0
+    cluster_m: int = 2
+    cluster_n: int = 1
+    sched: int = 0
+    split_k: int = 0
+    raster: int = 0
+    group: int = 0
+    c_col_major: int = 0
+    max_ctas: int = 0
+
+    def _c(self) -> _Cfg:
+        return _Cfg(self.block_m, self.block_n, self.block_k, self.stages, self.cluster_m,
+                    self.cluster_n, self.sched, self.split_k, self.raster, self.group,
+                    self.c_col_major, self.max_ctas)
+
+
+def library() -> ctypes.CDLL:
+    """Loads libb200gemm.so; raises if it has not been built (there is no fallback)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        raise GemmError(-1, f"{_LIB_PATH} is missing: run `python -m h100_gemm_b200.build`")
+    lib = ctypes.CDLL(str(_LIB_PATH))
+    vp, ci, cf, ll, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_size_t
+    cfgp = ctypes.POINTER(_Cfg)
+    lib.b200_gemm_bf16.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf, cfgp, vp, sz, vp]
+    lib.b200_gemm_bf16.restype = ci
+    lib.b200_gemm_batched_bf16.argtypes = [ci, ci, ci, ci, vp, ll, vp, ll, vp, ll, cf, cf, cfgp, vp, sz, vp]
+    lib.b200_gemm_batched_bf16.restype = ci
+    lib.b200_gemm_workspace_bytes.argtypes = [ci, ci, ci, ci, cfgp]
+    lib.b200_gemm_workspace_bytes.restype = sz
+    lib.b200_gemm_default_cfg.argtypes = [ci, ci, ci, ci, cfgp]
+    lib.b200_gemm_default_cfg.restype = ci
+    lib.b200_run_kernel.argtypes = [ci, ci, ci, vp, vp, vp, vp]
+    lib.b200_run_kernel.restype = ci
+    lib.b200_gemm_bf16_host.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf, cfgp]
+    lib.b200_gemm_bf16_host.restype = ci
+    lib.b200_gemm_host_release.argtypes = []
+    lib.b200_gemm_host_release.restype = None
+    lib.b200_reference_gpu_gemm_bf16.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf, vp]
+    lib.b200_reference_gpu_gemm_bf16.restype = ci
+    lib.b200_gemm_last_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint * 4)]
+    lib.b200_gemm_last_device_status.restype = ci
+    lib.b200_gemm_strerror.argtypes = [ci]
+    lib.b200_gemm_strerror.restype = ctypes.c_char_p
+    lib.b200_gemm_last_cuda_error.argtypes = []
+    lib.b200_gemm_last_cuda_error.restype = ci
+    lib.b200_gemm_sm_count.argtypes = []
+    lib.b200_gemm_sm_count.restype = ci
+    _lib = lib
+    return lib
+
+
+def _check(status: int) -> None:
+    if status != STATUS_OK:
+        lib = library()
+        msg = lib.b200_gemm_strerror(status).decode()
+        if status == STATUS_CUDA:
+            msg += f" (CUDA error {lib.b200_gemm_last_cuda_error()})"
+        raise GemmError(status, msg)
+
+
+def _cfg_ptr(cfg: Optional[GemmConfig]):
+    if cfg is None:
+        return None, None
+    c = cfg._c()
+    return c, ctypes.byref(c)
+
+
+def _stream_ptr(stream) -> Optional[int]:
+    if stream is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream or None
+    return getattr(stream, "cuda_stream", stream) or None
+
+
+def _require_cuda_bf16(t, name: str, ndim: int):
+    import torch
+    if not t.is_cuda:
+        raise GemmError(STATUS_INVALID_ARG, f"{name} must be a CUDA tensor (no CPU fallback exists)")
+    if t.dtype != torch.bfloat16 or t.dim() != ndim or not t.is_contiguous():
+        raise GemmError(STATUS_INVALID_ARG, f"{name} must be a contiguous {ndim}-D bfloat16 tensor")
+
+
+def workspace_bytes(batch: int, M: int, N: int, K: int, cfg: Optional[GemmConfig] = None) -> int:
+    keep, p = _cfg_ptr(cfg)
+    return int(library().b200_gemm_workspace_bytes(batch, M, N, K, p))
+
+
+def default_config(batch: int, M: int, N: int, K: int) -> GemmConfig:
+    c = _Cfg()
+    _check(library().b200_gemm_default_cfg(batch, M, N, K, ctypes.byref(c)))
+    return GemmConfig(**{n: getattr(c, n) for n, _ in _Cfg._fields_})
+
+
+def _workspace(nbytes: int, workspace, device):
+    import torch
+    if nbytes == 0:
+        return None, 0
+    if workspace is None:
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    if workspace.numel() * workspace.element_size() < nbytes:
+        raise GemmError(STATUS_WORKSPACE, f"workspace needs {nbytes} bytes")
+    return workspace, workspace.numel() * workspace.element_size()
+
+
+def gemm(a, b, out=None, alpha: float = 1.0, beta: float = 0.0, cfg: Optional[GemmConfig] = None,
+         workspace=None, stream=None):
+    """out[M,N] = (bf16)(a[M,K] @ b[N,K]^T * alpha + beta) on the current CUDA device.
+
+    With ``cfg.c_col_major`` the result is written column-major: ``out`` must then have shape
+    [N, M] (it holds C^T row-major), as matmulKernel of the reference does (matmul_utils.cuh:529).
+    """
+    import torch
+    _require_cuda_bf16(a, "a", 2)
+    _require_cuda_bf16(b, "b", 2)
+    M, K = a.shape
+    N, Kb = b.shape
+    if K != Kb:
+        raise GemmError(STATUS_INVALID_ARG, "a and b disagree on K")
+    col_major = bool(cfg is not None and cfg.c_col_major)
+    shape = (N, M) if col_major else (M, N)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.bfloat16, device=a.device)
+    _require_cuda_bf16(out, "out", 2)
+    if tuple(out.shape) != shape:
+        raise GemmError(STATUS_INVALID_ARG, f"out must have shape {shape}")
+    ws, ws_bytes = _workspace(workspace_bytes(1, M, N, K, cfg), workspace, a.device)
+    keep, p = _cfg_ptr(cfg)
+    _check(library().b200_gemm_bf16(M, N, K, a.data_ptr(), b.data_ptr(), out.data_ptr(), alpha, beta,
+                                    p, ws.data_ptr() if ws is not None else None, ws_bytes,
+                                    _stream_ptr(stream)))
+    return out
+
+
+def gemm_batched(a, b, out=None, alpha: float = 1.0, beta: float = 0.0,
+                 cfg: Optional[GemmConfig] = None, workspace=None, stream=None):
+    """out[i] = a[i] @ b[i]^T for contiguous [batch, M, K] and [batch, N, K] tensors."""
+    import torch
+    _require_cuda_bf16(a, "a", 3)
+    _require_cuda_bf16(b, "b", 3)
+    batch, M, K = a.shape
+    batch_b, N, Kb = b.shape
+    if K != Kb or batch != batch_b:
+        raise GemmError(STATUS_INVALID_ARG, "a and b disagree on batch or K")
+    if out is None:
+        out = torch.empty((batch, M, N), dtype=torch.bfloat16, device=a.device)
+    _require_cuda_bf16(out, "out", 3)
+    ws, ws_bytes = _workspace(workspace_bytes(batch, M, N, K, cfg), workspace, a.device)
+    keep, p = _cfg_ptr(cfg)
+    _check(library().b200_gemm_batched_bf16(
+        batch, M, N, K, a.data_ptr(), M * K, b.data_ptr(), N * K, out.data_ptr(), M * N, alpha, beta, p,
+        ws.data_ptr() if ws is not None else None, ws_bytes, _stream_ptr(stream)))
+    return out
+
+
+def run_kernel(a, b, out=None):
+    """runKernel(M, N, K, A, B, C, DB): default configuration, column-major C, default stream.
+
+    ``out`` has shape [N, M] (C^T row-major == C column-major with leading dimension M).
+    """
+    import torch
+    _require_cuda_bf16(a, "a", 2)
+    _require_cuda_bf16(b, "b", 2)
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty((N, M), dtype=torch.bfloat16, device=a.device)
+    torch.cuda.current_stream().synchronize()
+    _check(library().b200_run_kernel(M, N, K, a.data_ptr(), b.data_ptr(), out.data_ptr(), None))
+    torch.cuda.synchronize()
+    return out
+
+
+def reference_gpu_gemm(a, b, out=None, alpha: float = 1.0, beta: float = 0.0, stream=None):
+    """The slow SIMT cross-check GEMM (reference.h:78-90 semantics), row-major C."""
+    import torch
+    _require_cuda_bf16(a, "a", 2)
+    _require_cuda_bf16(b, "b", 2)
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    _check(library().b200_reference_gpu_gemm_bf16(M, N, K, a.data_ptr(), b.data_ptr(), out.data_ptr(),
+                                                  alpha, beta, _stream_ptr(stream)))
+    return out
+
+
+def gemm_host(a_bits, b_bits, out_bits=None, alpha: float = 1.0, beta: float = 0.0,
+              cfg: Optional[GemmConfig] = None):
+    """Host-buffer GEMM: numpy uint16 arrays holding bf16 bit patterns, [M,K] and [N,K].
+
+    Copies to the device, multiplies and copies back inside the library (b200_gemm_bf16_host).
+    Accepts torch CPU tensors (pinned or not) of dtype bfloat16 as well.
+    """
+    import numpy as np
+
+    def ptr_shape(x):
+        if isinstance(x, np.ndarray):
+            if x.dtype != np.uint16 or not x.flags.c_contiguous:
+                raise GemmError(STATUS_INVALID_ARG, "numpy operands must be C-contiguous uint16")
+            return x.ctypes.data, x.shape
+        return x.data_ptr(), tuple(x.shape)
+
+    pa, (M, K) = ptr_shape(a_bits)
+    pb, (N, Kb) = ptr_shape(b_bits)
+    if K != Kb:
+        raise GemmError(STATUS_INVALID_ARG, "a and b disagree on K")
+    if out_bits is None:
+        if isinstance(a_bits, np.ndarray):
+            out_bits = np.empty((M, N), dtype=np.uint16)
+        else:
+            import torch
+            out_bits = torch.empty((M, N), dtype=a_bits.dtype, pin_memory=a_bits.is_pinned())
+    pc, _ = ptr_shape(out_bits)
+    keep, p = _cfg_ptr(cfg)
+    _check(library().b200_gemm_bf16_host(M, N, K, pa, pb, pc, alpha, beta, p))
+    return out_bits
+
+
+def device_status():
+    """Synchronises and returns (status_code, [role, block, tile, detail])."""
+    words = (ctypes.c_uint * 4)()
+    rc = library().b200_gemm_last_device_status(ctypes.byref(words))
+    if rc not in (STATUS_OK, STATUS_DEVICE_TIMEOUT):
+        _check(rc)
+    return rc, list(words)

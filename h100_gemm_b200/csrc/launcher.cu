@@ -1,0 +1,797 @@
+// Host launcher and C ABI (include/b200_gemm.h) of the sm_100a GEMM.
+//
+// Replaces the reference's host launchers gpu_gemm() (matmul_h100.cu.jinja:927-985) and
+// runKernel() (matmul_h100_optimal.cu:32-59) and its tensor-map builder make_tma_copy_desc()
+// (tma.cuh:83-181). Differences that matter to a caller:
+//   * errors are returned, never exit()/assert();
+//   * tensor maps and function attributes are cached instead of being rebuilt inside the timed
+//     loop (matmul_h100.cu.jinja:938-957);
+//   * the grid is sized from the device (SM count, co-resident clusters) instead of the
+//     hard-coded NUM_SM = 128 (matmul_h100_optimal.cu:40).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <tuple>
+#include <vector>
+
+#include "../../include/b200_gemm.h"
+#include "sm100/gemm_kernel.cuh"
+
+namespace {
+
+using namespace b200;
+
+thread_local int g_last_cuda_error = 0;
+
+#define B200_CUDA_TRY(expr)                           \
+  do {                                                \
+    cudaError_t e__ = (expr);                         \
+    if (e__ != cudaSuccess) {                         \
+      g_last_cuda_error = static_cast<int>(e__);      \
+      (void)cudaGetLastError();                       \
+      return B200_ERR_CUDA;                           \
+    }                                                 \
+  } while (0)
+
+// Device-side status word (one per device that loads this library).
+__device__ unsigned int g_device_status[4];
+
+// ------------------------------------------------------------------------------------------
+// Auxiliary kernels
+// ------------------------------------------------------------------------------------------
+
+// Copies rows of K 16-bit elements to a pitch of Kp elements (Kp % 8 == 0) so that the copy can
+// be read through a tensor map. Elements K..Kp-1 are never read (the map's extent stays K).
+__global__ void repitch_rows_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst,
+                                    long long rows, int K, int Kp) {
+  const long long total = rows * K;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / K;
+    const int k = static_cast<int>(i - r * K);
+    dst[r * Kp + k] = src[i];
+  }
+}
+
+// Sums the fp32 partial slots of every split tile in slot order and writes the bf16 result.
+__global__ void fixup_kernel(GemmArgs args, int block_m, int block_n) {
+  __shared__ int slots[64];
+  __shared__ int nslots;
+  for (int tile = blockIdx.x; tile < args.sched.num_tiles; tile += gridDim.x) {
+    __syncthreads();
+    if (threadIdx.x == 0) nslots = tile_partial_slots(args.sched, tile, slots, 64);
+    __syncthreads();
+    const int n = nslots;
+    if (n == 0) continue;
+    const TileCoord tc = tile_coord(args.sched, tile);
+    const int m0 = tc.m * block_m;
+    const int n0 = tc.n * block_n;
+    const int rows = min(block_m, args.M - m0);
+    const int vec_per_row = block_n / 4;
+    const long long slot_elems = static_cast<long long>(block_m) * block_n;
+    for (int idx = threadIdx.x; idx < rows * vec_per_row; idx += blockDim.x) {
+      const int r = idx / vec_per_row;
+      const int c = (idx - r * vec_per_row) * 4;
+      if (n0 + c >= args.N) continue;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < n; ++s) {
+        const float4 p = *reinterpret_cast<const float4*>(
+            args.partial + slots[s] * slot_elems + static_cast<long long>(r) * block_n + c);
+        acc.x += p.x;
+        acc.y += p.y;
+        acc.z += p.z;
+        acc.w += p.w;
+      }
+      float v[4] = {acc.x, acc.y, acc.z, acc.w};
+      __nv_bfloat16* dst =
+          args.C + tc.b * args.c_batch_stride + static_cast<long long>(m0 + r) * args.ldc + n0 + c;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (n0 + c + j < args.N) {
+          float x = v[j];
+          if (args.scale) x = __fadd_rn(__fmul_rn(x, args.alpha), args.beta);
+          dst[j] = __float2bfloat16_rn(x);
+        }
+      }
+    }
+  }
+}
+
+// Plain SIMT GEMM, the on-device cross-check (semantics of reference.h:49-76: k ascending, fp32
+// accumulate, (bf16)(acc * alpha + beta)); one thread per 4x4 outputs.
+__global__ void naive_gemm_kernel(int M, int N, int K, const __nv_bfloat16* __restrict__ A,
+                                  const __nv_bfloat16* __restrict__ B, __nv_bfloat16* __restrict__ C,
+                                  float alpha, float beta) {
+  const int n0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const int m0 = blockIdx.y * 4;
+  if (n0 >= N || m0 >= M) return;
+  float acc[4][4] = {};
+  for (int k = 0; k < K; ++k) {
+    float a[4], b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      a[i] = m0 + i < M ? __bfloat162float(A[static_cast<long long>(m0 + i) * K + k]) : 0.f;
+      b[i] = n0 + i < N ? __bfloat162float(B[static_cast<long long>(n0 + i) * K + k]) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+  }
+  for (int i = 0; i < 4; ++i)
+    for (int j = 0; j < 4; ++j)
+      if (m0 + i < M && n0 + j < N)
+        C[static_cast<long long>(m0 + i) * N + n0 + j] =
+            __float2bfloat16_rn(__fadd_rn(__fmul_rn(acc[i][j], alpha), beta));
+}
+
+// ------------------------------------------------------------------------------------------
+// Kernel table
+// ------------------------------------------------------------------------------------------
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmArgs);
+
+struct KernelEntry {
+  int bn;
+  int pair;
+  KernelFn fn;
+  int stage_bytes;
+  int max_stages;
+  int b_rows_cta;
+};
+
+template <int BN, int PAIR>
+KernelEntry make_entry() {
+  using T = KernelTraits<BN, PAIR>;
+  return KernelEntry{BN, PAIR, &gemm_kernel<BN, PAIR>, T::kStageBytes, T::max_stages(),
+                     T::kBRowsCta};
+}
+
+const KernelEntry* find_kernel(int bn, int pair) {
+  static const KernelEntry table[] = {
+      make_entry<64, 0>(),  make_entry<128, 0>(), make_entry<192, 0>(), make_entry<256, 0>(),
+      make_entry<64, 1>(),  make_entry<128, 1>(), make_entry<192, 1>(), make_entry<256, 1>(),
+  };
+  for (const auto& e : table)
+    if (e.bn == bn && e.pair == pair) return &e;
+  return nullptr;
+}
+
+int smem_bytes_for(const KernelEntry& e, int stages) {
+  return 1024 + stages * e.stage_bytes + kEpiBytes + kBarrierBytes;
+}
+
+// ------------------------------------------------------------------------------------------
+// Per-device state
+// ------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int smem_optin = 0;
+  unsigned int* status = nullptr;
+  std::map<std::tuple<const void*, int>, int> max_workers;  // (kernel, smem) -> co-resident workers
+};
+
+std::mutex g_mutex;
+DeviceState g_devices[64];
+EncodeTiledFn g_encode = nullptr;
+
+int get_device_state(DeviceState** out) {
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return B200_ERR_INVALID_ARG;
+  DeviceState& st = g_devices[dev];
+  if (!st.ready) {
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&st.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    void* p = nullptr;
+    B200_CUDA_TRY(cudaGetSymbolAddress(&p, g_device_status));
+    st.status = static_cast<unsigned int*>(p);
+    B200_CUDA_TRY(cudaMemset(st.status, 0, sizeof(unsigned int) * 4));
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      B200_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+      if (fn == nullptr || qres != cudaDriverEntryPointSuccess) {
+        g_last_cuda_error = static_cast<int>(cudaErrorNotSupported);
+        return B200_ERR_CUDA;
+      }
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    st.ready = true;
+  }
+  *out = &st;
+  return B200_OK;
+}
+
+// Workers (CTAs, or CTA pairs) that can be resident at once for this kernel and smem size.
+int max_resident_workers(DeviceState& st, const KernelEntry& e, int smem, int* out) {
+  auto key = std::make_tuple(reinterpret_cast<const void*>(e.fn), smem);
+  auto it = st.max_workers.find(key);
+  if (it != st.max_workers.end()) {
+    *out = it->second;
+    return B200_OK;
+  }
+  // Opt in to the device maximum once, so a later launch with fewer stages cannot shrink it.
+  B200_CUDA_TRY(cudaFuncSetAttribute(e.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+  if (smem > st.smem_optin) return B200_ERR_SMEM;
+  int workers = st.sm_count;
+  if (e.pair) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(st.sm_count & ~1), 1, 1);
+    cfg.blockDim = dim3(kNumThreads, 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    B200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, e.fn, &cfg));
+    workers = clusters;
+  }
+  if (workers <= 0) return B200_ERR_SMEM;
+  st.max_workers[key] = workers;
+  *out = workers;
+  return B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Tensor maps (bf16, rank 3: {inner, rows, batch}), 128-byte swizzle, zero fill out of bounds
+// ------------------------------------------------------------------------------------------
+struct MapKey {
+  const void* base;
+  uint64_t inner, rows, batch, pitch_bytes, batch_pitch_bytes;
+  uint32_t box_inner, box_rows;
+  bool operator<(const MapKey& o) const {
+    return std::tie(base, inner, rows, batch, pitch_bytes, batch_pitch_bytes, box_inner, box_rows) <
+           std::tie(o.base, o.inner, o.rows, o.batch, o.pitch_bytes, o.batch_pitch_bytes,
+                    o.box_inner, o.box_rows);
+  }
+};
+std::map<MapKey, CUtensorMap> g_map_cache;
+
+int make_tensor_map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows,
+                    uint64_t batch, uint64_t pitch_bytes, uint64_t batch_pitch_bytes,
+                    uint32_t box_inner, uint32_t box_rows) {
+  MapKey key{base, inner, rows, batch, pitch_bytes, batch_pitch_bytes, box_inner, box_rows};
+  auto it = g_map_cache.find(key);
+  if (it != g_map_cache.end()) {
+    *out = it->second;
+    return B200_OK;
+  }
+  cuuint64_t dims[3] = {inner, rows, batch};
+  cuuint64_t strides[2] = {pitch_bytes, batch > 1 ? batch_pitch_bytes : pitch_bytes * rows};
+  if (strides[1] % 16 != 0) strides[1] = (strides[1] + 15) / 16 * 16;  // unused when batch == 1
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t elem_strides[3] = {1, 1, 1};
+  CUtensorMap m;
+  CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
+                        strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return B200_ERR_CUDA;
+  }
+  if (g_map_cache.size() >= 256) g_map_cache.clear();
+  g_map_cache[key] = m;
+  *out = m;
+  return B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Configuration
+// ------------------------------------------------------------------------------------------
+struct Plan {
+  const KernelEntry* kernel;
+  int pair;
+  int stages;
+  int smem;
+  int mode;
+  int split_k;
+  int raster;
+  int group;
+  int max_ctas;
+  int c_col_major;
+};
+
+b200_gemm_cfg default_cfg(int batch, int M, int N, int K) {
+  (void)batch;
+  (void)K;
+  b200_gemm_cfg c;
+  std::memset(&c, 0, sizeof(c));
+  c.block_m = 128;
+  c.block_k = 64;
+  c.cluster_n = 1;
+  c.group = 8;
+  if (M > 128) {
+    c.cluster_m = 2;
+    c.block_n = N > 128 ? 256 : 128;
+  } else {
+    // Few rows: one CTA per tile, narrower tiles, and an even split of the K loop over all SMs
+    // so that every SM streams the same share of B.
+    c.cluster_m = 1;
+    c.block_n = 128;
+    c.sched = kStreamK;
+  }
+  return c;
+}
+
+int resolve_plan(const b200_gemm_cfg& c, Plan* p) {
+  if (c.block_k != 0 && c.block_k != 64) return B200_ERR_UNSUPPORTED_CFG;
+  if (c.block_m != 0 && c.block_m != 128) return B200_ERR_UNSUPPORTED_CFG;
+  if (c.cluster_n != 0 && c.cluster_n != 1) return B200_ERR_UNSUPPORTED_CFG;
+  int cm = c.cluster_m == 0 ? 1 : c.cluster_m;
+  if (cm < 1 || cm > 16 || (cm & (cm - 1)) != 0) return B200_ERR_UNSUPPORTED_CFG;
+  const int bn = c.block_n == 0 ? 128 : c.block_n;
+  p->pair = cm >= 2 ? 1 : 0;
+  p->kernel = find_kernel(bn, p->pair);
+  if (p->kernel == nullptr) return B200_ERR_UNSUPPORTED_CFG;
+  if (c.stages < 0) return B200_ERR_INVALID_ARG;
+  p->stages = c.stages == 0 ? p->kernel->max_stages : c.stages;
+  if (p->stages > kMaxStages) return B200_ERR_UNSUPPORTED_CFG;
+  if (p->stages < 2) return B200_ERR_UNSUPPORTED_CFG;
+  if (p->stages > p->kernel->max_stages) return B200_ERR_SMEM;
+  p->smem = smem_bytes_for(*p->kernel, p->stages);
+  if (c.sched < 0 || c.sched > 2) return B200_ERR_INVALID_ARG;
+  p->mode = c.sched;
+  p->split_k = c.split_k <= 1 ? 1 : c.split_k;
+  if (p->split_k > 64) return B200_ERR_UNSUPPORTED_CFG;
+  if (p->mode == kSplitK && p->split_k == 1) p->mode = kDataParallel;
+  p->raster = c.raster ? 1 : 0;
+  p->group = c.group > 0 ? c.group : 8;
+  if (cm > 2) p->group = p->group * (cm / 2);
+  p->max_ctas = c.max_ctas;
+  p->c_col_major = c.c_col_major ? 1 : 0;
+  return B200_OK;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct Problem {
+  int batch, M, N, K;          // as the kernel sees them (after a column-major swap)
+  const void* A;
+  const void* B;
+  void* C;
+  long long strideA, strideB, strideC;
+};
+
+// Workspace layout: [fp32 partial slots][re-pitched A][re-pitched B]
+struct WorkspaceLayout {
+  size_t partial_bytes;
+  size_t a_bytes;
+  size_t b_bytes;
+  int k_pitch;
+  bool repitch;
+  size_t total() const { return partial_bytes + a_bytes + b_bytes; }
+};
+
+bool needs_repitch(const Problem& pr) {
+  if (pr.K % 8 != 0) return true;
+  if ((reinterpret_cast<uintptr_t>(pr.A) & 15u) || (reinterpret_cast<uintptr_t>(pr.B) & 15u)) return true;
+  if (pr.batch > 1 && ((pr.strideA % 8) || (pr.strideB % 8))) return true;
+  return false;
+}
+
+void build_sched(const Plan& p, const Problem& pr, int workers, SchedParams* s) {
+  const int block_m = kCtaRows * (p.pair ? 2 : 1);
+  s->tiles_m = (pr.M + block_m - 1) / block_m;
+  s->tiles_n = (pr.N + p.kernel->bn - 1) / p.kernel->bn;
+  s->batch = pr.batch;
+  s->num_tiles = s->tiles_m * s->tiles_n * pr.batch;
+  s->k_tiles = (pr.K + kBlockK - 1) / kBlockK;
+  s->group = p.group;
+  s->raster = p.raster;
+  s->mode = p.mode;
+  s->split_k = p.split_k;
+  if (s->mode == kSplitK && s->split_k > s->k_tiles) s->split_k = s->k_tiles;
+  if (s->mode == kSplitK && s->split_k <= 1) {
+    s->mode = kDataParallel;
+    s->split_k = 1;
+  }
+  long long units = s->num_tiles;
+  if (s->mode == kSplitK) units *= s->split_k;
+  if (s->mode == kStreamK) units = sched_total_iters(*s);
+  s->num_workers = static_cast<int>(units < workers ? units : workers);
+  if (s->num_workers < 1) s->num_workers = 1;
+}
+
+WorkspaceLayout workspace_layout(const Plan& p, const Problem& pr, const SchedParams& s) {
+  WorkspaceLayout w{};
+  const int block_m = kCtaRows * (p.pair ? 2 : 1);
+  w.partial_bytes =
+      align_up(static_cast<size_t>(sched_num_slots(s)) * block_m * p.kernel->bn * sizeof(float), 256);
+  w.repitch = needs_repitch(pr);
+  w.k_pitch = (pr.K + 7) / 8 * 8;
+  if (w.repitch) {
+    w.a_bytes = align_up(static_cast<size_t>(pr.batch) * pr.M * w.k_pitch * 2, 256);
+    w.b_bytes = align_up(static_cast<size_t>(pr.batch) * pr.N * w.k_pitch * 2, 256);
+  }
+  return w;
+}
+
+int nominal_workers(const Plan& p, int sm_count) {
+  int w = p.pair ? sm_count / 2 : sm_count;
+  if (p.max_ctas > 0) {
+    const int cap = p.pair ? p.max_ctas / 2 : p.max_ctas;
+    if (cap < w) w = cap;
+  }
+  return w < 1 ? 1 : w;
+}
+
+int validate(int batch, int M, int N, int K, const void* A, const void* B, const void* C) {
+  if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARG;
+  if (A == nullptr || B == nullptr || C == nullptr) return B200_ERR_INVALID_ARG;
+  return B200_OK;
+}
+
+int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, const void* B,
+             long long strideB, void* C, long long strideC, float alpha, float beta,
+             const b200_gemm_cfg* user_cfg, void* workspace, size_t workspace_bytes,
+             cudaStream_t stream) {
+  int rc = validate(batch, M, N, K, A, B, C);
+  if (rc != B200_OK) return rc;
+  b200_gemm_cfg cfg = user_cfg ? *user_cfg : default_cfg(batch, M, N, K);
+  if (user_cfg == nullptr && M <= 128 && N > 128) {
+    // nothing: default_cfg already chose the few-rows plan
+  }
+  Plan plan;
+  rc = resolve_plan(cfg, &plan);
+  if (rc != B200_OK) return rc;
+
+  Problem pr{batch, M, N, K, A, B, C, strideA, strideB, strideC};
+  if (plan.c_col_major) {
+    // Column-major C[M,N] (ld M) is row-major C^T[N,M] = B * A^T: swap the operands.
+    pr.M = N;
+    pr.N = M;
+    pr.A = B;
+    pr.B = A;
+    pr.strideA = strideB;
+    pr.strideB = strideA;
+  }
+
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState* st = nullptr;
+  rc = get_device_state(&st);
+  if (rc != B200_OK) return rc;
+
+  int resident = 0;
+  rc = max_resident_workers(*st, *plan.kernel, plan.smem, &resident);
+  if (rc != B200_OK) return rc;
+  int workers = nominal_workers(plan, st->sm_count);
+  if (workers > resident) workers = resident;
+
+  GemmArgs args;
+  std::memset(&args, 0, sizeof(args));
+  build_sched(plan, pr, workers, &args.sched);
+  const WorkspaceLayout ws = workspace_layout(plan, pr, args.sched);
+  if (ws.total() > 0 && (workspace == nullptr || workspace_bytes < ws.total())) return B200_ERR_WORKSPACE;
+  if (ws.total() > 0 && (reinterpret_cast<uintptr_t>(workspace) & 255u)) return B200_ERR_INVALID_ARG;
+
+  const void* a_src = pr.A;
+  const void* b_src = pr.B;
+  long long a_pitch = pr.K, b_pitch = pr.K;
+  long long a_bstride = pr.strideA, b_bstride = pr.strideB;
+  if (ws.repitch) {
+    uint8_t* base = static_cast<uint8_t*>(workspace) + ws.partial_bytes;
+    uint16_t* a_dst = reinterpret_cast<uint16_t*>(base);
+    uint16_t* b_dst = reinterpret_cast<uint16_t*>(base + ws.a_bytes);
+    const int threads = 256;
+    for (int b = 0; b < pr.batch; ++b) {
+      const long long rows_a = pr.M, rows_b = pr.N;
+      const int blocks_a = static_cast<int>(std::min<long long>((rows_a * pr.K + threads - 1) / threads, 148 * 16));
+      const int blocks_b = static_cast<int>(std::min<long long>((rows_b * pr.K + threads - 1) / threads, 148 * 16));
+      repitch_rows_kernel<<<blocks_a, threads, 0, stream>>>(
+          static_cast<const uint16_t*>(pr.A) + b * pr.strideA,
+          a_dst + static_cast<long long>(b) * pr.M * ws.k_pitch, rows_a, pr.K, ws.k_pitch);
+      repitch_rows_kernel<<<blocks_b, threads, 0, stream>>>(
+          static_cast<const uint16_t*>(pr.B) + b * pr.strideB,
+          b_dst + static_cast<long long>(b) * pr.N * ws.k_pitch, rows_b, pr.K, ws.k_pitch);
+    }
+    B200_CUDA_TRY(cudaGetLastError());
+    a_src = a_dst;
+    b_src = b_dst;
+    a_pitch = b_pitch = ws.k_pitch;
+    a_bstride = static_cast<long long>(pr.M) * ws.k_pitch;
+    b_bstride = static_cast<long long>(pr.N) * ws.k_pitch;
+  }
+
+  // C can be written by TMA when its row pitch, base and batch pitch are 16-byte aligned.
+  const bool c_tma = (pr.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(pr.C) & 15u) == 0) &&
+                     (pr.batch == 1 || pr.strideC % 8 == 0);
+
+  CUtensorMap map_a, map_b, map_c;
+  rc = make_tensor_map(&map_a, a_src, pr.K, pr.M, pr.batch, a_pitch * 2, a_bstride * 2, kBlockK, kCtaRows);
+  if (rc != B200_OK) return rc;
+  rc = make_tensor_map(&map_b, b_src, pr.K, pr.N, pr.batch, b_pitch * 2, b_bstride * 2, kBlockK,
+                       plan.kernel->b_rows_cta);
+  if (rc != B200_OK) return rc;
+  if (c_tma) {
+    rc = make_tensor_map(&map_c, pr.C, pr.N, pr.M, pr.batch, static_cast<uint64_t>(pr.N) * 2,
+                         pr.strideC * 2, kEpiChunkCols, 32);
+    if (rc != B200_OK) return rc;
+  } else {
+    map_c = map_a;  // never dereferenced by the store path
+  }
+
+  args.M = pr.M;
+  args.N = pr.N;
+  args.K = pr.K;
+  args.batch = pr.batch;
+  args.stages = plan.stages;
+  args.c_direct = c_tma ? 0 : 1;
+  args.C = static_cast<__nv_bfloat16*>(pr.C);
+  args.ldc = pr.N;
+  args.c_batch_stride = pr.strideC;
+  args.partial = ws.partial_bytes ? static_cast<float*>(workspace) : nullptr;
+  args.alpha = alpha;
+  args.beta = beta;
+  args.scale = (alpha != 1.0f || beta != 0.0f) ? 1 : 0;
+  args.status = st->status;
+
+  cudaLaunchConfig_t lc = {};
+  const int ctas = args.sched.num_workers * (plan.pair ? 2 : 1);
+  lc.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
+  lc.blockDim = dim3(kNumThreads, 1, 1);
+  lc.dynamicSmemBytes = static_cast<size_t>(plan.smem);
+  lc.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = plan.pair ? 2 : 1;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  lc.attrs = &attr;
+  lc.numAttrs = 1;
+  B200_CUDA_TRY(cudaLaunchKernelEx(&lc, plan.kernel->fn, map_a, map_b, map_c, args));
+
+  if (sched_num_slots(args.sched) > 0) {
+    const int block_m = kCtaRows * (plan.pair ? 2 : 1);
+    const int blocks = args.sched.num_tiles < st->sm_count * 4 ? args.sched.num_tiles : st->sm_count * 4;
+    fixup_kernel<<<blocks, 256, 0, stream>>>(args, block_m, plan.kernel->bn);
+    B200_CUDA_TRY(cudaGetLastError());
+  }
+  return B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Host-buffer path: device staging buffers kept between calls
+// ------------------------------------------------------------------------------------------
+struct HostPath {
+  void* dA = nullptr;
+  void* dB = nullptr;
+  void* dC = nullptr;
+  void* ws = nullptr;
+  size_t a_cap = 0, b_cap = 0, c_cap = 0, ws_cap = 0;
+  cudaStream_t copy_in = nullptr, compute = nullptr, copy_out = nullptr;
+  std::vector<cudaEvent_t> events;
+  int device = -1;
+};
+HostPath g_host;
+
+int grow(void** p, size_t* cap, size_t need) {
+  if (need <= *cap) return B200_OK;
+  if (*p) B200_CUDA_TRY(cudaFree(*p));
+  *p = nullptr;
+  *cap = 0;
+  B200_CUDA_TRY(cudaMalloc(p, need));
+  *cap = need;
+  return B200_OK;
+}
+
+}  // namespace
+
+// ==========================================================================================
+// C ABI
+// ==========================================================================================
+extern "C" {
+
+int b200_gemm_bf16(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
+                   float beta, const b200_gemm_cfg* cfg, void* workspace, size_t workspace_bytes,
+                   void* stream) {
+  return run_gemm(1, M, N, K, A, 0, B, 0, C, 0, alpha, beta, cfg, workspace, workspace_bytes,
+                  static_cast<cudaStream_t>(stream));
+}
+
+int b200_gemm_batched_bf16(int batch, int M, int N, int K, const void* A, long long strideA,
+                           const void* B, long long strideB, void* C, long long strideC,
+                           float alpha, float beta, const b200_gemm_cfg* cfg, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  if (cfg != nullptr && cfg->c_col_major && batch > 1) return B200_ERR_UNSUPPORTED_CFG;
+  return run_gemm(batch, M, N, K, A, strideA, B, strideB, C, strideC, alpha, beta, cfg, workspace,
+                  workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200_gemm_workspace_bytes(int batch, int M, int N, int K, const b200_gemm_cfg* user_cfg) {
+  if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
+  b200_gemm_cfg cfg = user_cfg ? *user_cfg : default_cfg(batch, M, N, K);
+  Plan plan;
+  if (resolve_plan(cfg, &plan) != B200_OK) return 0;
+  Problem pr{batch, M, N, K, reinterpret_cast<const void*>(16), reinterpret_cast<const void*>(16),
+             nullptr, 8, 8, 8};
+  if (plan.c_col_major) {
+    pr.M = N;
+    pr.N = M;
+  }
+  // Without a device, size for a full B200 (148 SMs); the launcher re-checks against the real
+  // grid and reports B200_ERR_WORKSPACE if the buffer is too small.
+  int sm = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) sm = v;
+  } else {
+    (void)cudaGetLastError();
+  }
+  SchedParams s;
+  build_sched(plan, pr, nominal_workers(plan, sm), &s);
+  return workspace_layout(plan, pr, s).total();
+}
+
+int b200_gemm_default_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg) {
+  if (cfg == nullptr || batch <= 0 || M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARG;
+  *cfg = default_cfg(batch, M, N, K);
+  Plan plan;
+  int rc = resolve_plan(*cfg, &plan);
+  if (rc != B200_OK) return rc;
+  cfg->stages = plan.stages;
+  return B200_OK;
+}
+
+int b200_run_kernel(int M, int N, int K, void* A, void* B, void* C, int* DB) {
+  (void)DB;
+  if (M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARG;
+  b200_gemm_cfg cfg = default_cfg(1, N, M, K);  // shape as the kernel sees it after the swap
+  cfg.sched = kDataParallel;
+  cfg.c_col_major = 1;
+  return run_gemm(1, M, N, K, A, 0, B, 0, C, 0, 1.0f, 0.0f, &cfg, nullptr, 0, nullptr);
+}
+
+int b200_reference_gpu_gemm_bf16(int M, int N, int K, const void* A, const void* B, void* C,
+                                 float alpha, float beta, void* stream) {
+  int rc = validate(1, M, N, K, A, B, C);
+  if (rc != B200_OK) return rc;
+  dim3 block(128, 1);
+  dim3 grid((N + 511) / 512, (M + 3) / 4);
+  naive_gemm_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+      M, N, K, static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(B),
+      static_cast<__nv_bfloat16*>(C), alpha, beta);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_gemm_bf16_host(int M, int N, int K, const void* hA, const void* hB, void* hC, float alpha,
+                        float beta, const b200_gemm_cfg* cfg) {
+  int rc = validate(1, M, N, K, hA, hB, hC);
+  if (rc != B200_OK) return rc;
+  if (cfg != nullptr && cfg->c_col_major) return B200_ERR_UNSUPPORTED_CFG;
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  HostPath& h = g_host;
+  if (h.device != dev) {
+    b200_gemm_host_release();
+    h.device = dev;
+  }
+  if (h.compute == nullptr) {
+    B200_CUDA_TRY(cudaStreamCreateWithFlags(&h.copy_in, cudaStreamNonBlocking));
+    B200_CUDA_TRY(cudaStreamCreateWithFlags(&h.compute, cudaStreamNonBlocking));
+    B200_CUDA_TRY(cudaStreamCreateWithFlags(&h.copy_out, cudaStreamNonBlocking));
+  }
+  const size_t a_bytes = static_cast<size_t>(M) * K * 2;
+  const size_t b_bytes = static_cast<size_t>(N) * K * 2;
+  const size_t c_bytes = static_cast<size_t>(M) * N * 2;
+  if ((rc = grow(&h.dA, &h.a_cap, a_bytes)) != B200_OK) return rc;
+  if ((rc = grow(&h.dB, &h.b_cap, b_bytes)) != B200_OK) return rc;
+  if ((rc = grow(&h.dC, &h.c_cap, c_bytes)) != B200_OK) return rc;
+
+  // Row bands of A (and C): band i+1 is copied in while band i is multiplied and band i-1 is
+  // copied out. Bands are multiples of 256 rows so every band tiles like the whole problem; a
+  // band must be worth a launch, hence at most 8 of them.
+  int bands = 1;
+  if (M >= 2048 && K % 8 == 0 && N % 8 == 0) bands = M >= 8192 ? 8 : 4;
+  const int band_rows = ((M + bands - 1) / bands + 255) / 256 * 256;
+  bands = (M + band_rows - 1) / band_rows;
+
+  size_t ws_need = 0;
+  for (int i = 0; i < bands; ++i) {
+    const int rows = std::min(band_rows, M - i * band_rows);
+    ws_need = std::max(ws_need, b200_gemm_workspace_bytes(1, rows, N, K, cfg));
+  }
+  if ((rc = grow(&h.ws, &h.ws_cap, ws_need)) != B200_OK) return rc;
+  while (static_cast<int>(h.events.size()) < 2 * bands + 1) {
+    cudaEvent_t e;
+    B200_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    h.events.push_back(e);
+  }
+
+  B200_CUDA_TRY(cudaMemcpyAsync(h.dB, hB, b_bytes, cudaMemcpyHostToDevice, h.copy_in));
+  for (int i = 0; i < bands; ++i) {
+    const int r0 = i * band_rows;
+    const int rows = std::min(band_rows, M - r0);
+    const size_t a_off = static_cast<size_t>(r0) * K * 2;
+    const size_t c_off = static_cast<size_t>(r0) * N * 2;
+    B200_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(h.dA) + a_off,
+                                  static_cast<const uint8_t*>(hA) + a_off,
+                                  static_cast<size_t>(rows) * K * 2, cudaMemcpyHostToDevice, h.copy_in));
+    B200_CUDA_TRY(cudaEventRecord(h.events[2 * i], h.copy_in));
+    B200_CUDA_TRY(cudaStreamWaitEvent(h.compute, h.events[2 * i], 0));
+    rc = run_gemm(1, rows, N, K, static_cast<uint8_t*>(h.dA) + a_off, 0, h.dB, 0,
+                  static_cast<uint8_t*>(h.dC) + c_off, 0, alpha, beta, cfg, h.ws, h.ws_cap, h.compute);
+    if (rc != B200_OK) return rc;
+    B200_CUDA_TRY(cudaEventRecord(h.events[2 * i + 1], h.compute));
+    B200_CUDA_TRY(cudaStreamWaitEvent(h.copy_out, h.events[2 * i + 1], 0));
+    B200_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(hC) + c_off, static_cast<uint8_t*>(h.dC) + c_off,
+                                  static_cast<size_t>(rows) * N * 2, cudaMemcpyDeviceToHost, h.copy_out));
+  }
+  B200_CUDA_TRY(cudaStreamSynchronize(h.copy_out));
+  B200_CUDA_TRY(cudaStreamSynchronize(h.compute));
+  B200_CUDA_TRY(cudaStreamSynchronize(h.copy_in));
+  return B200_OK;
+}
+
+void b200_gemm_host_release(void) {
+  HostPath& h = g_host;
+  if (h.dA) cudaFree(h.dA);
+  if (h.dB) cudaFree(h.dB);
+  if (h.dC) cudaFree(h.dC);
+  if (h.ws) cudaFree(h.ws);
+  for (cudaEvent_t e : h.events) cudaEventDestroy(e);
+  if (h.copy_in) cudaStreamDestroy(h.copy_in);
+  if (h.compute) cudaStreamDestroy(h.compute);
+  if (h.copy_out) cudaStreamDestroy(h.copy_out);
+  h = HostPath();
+  (void)cudaGetLastError();
+}
+
+int b200_gemm_last_device_status(unsigned int out[4]) {
+  if (out == nullptr) return B200_ERR_INVALID_ARG;
+  B200_CUDA_TRY(cudaDeviceSynchronize());
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState* st = nullptr;
+  int rc = get_device_state(&st);
+  if (rc != B200_OK) return rc;
+  B200_CUDA_TRY(cudaMemcpy(out, st->status, sizeof(unsigned int) * 4, cudaMemcpyDeviceToHost));
+  if (out[0] != 0) {
+    B200_CUDA_TRY(cudaMemset(st->status, 0, sizeof(unsigned int) * 4));
+    return B200_ERR_DEVICE_TIMEOUT;
+  }
+  return B200_OK;
+}
+
+const char* b200_gemm_strerror(int status) {
+  switch (status) {
+    case B200_OK: return "success";
+    case B200_ERR_INVALID_ARG: return "invalid argument";
+    case B200_ERR_UNSUPPORTED_CFG: return "unsupported tile/cluster/stage configuration";
+    case B200_ERR_SMEM: return "configuration exceeds shared memory";
+    case B200_ERR_WORKSPACE: return "workspace missing or too small";
+    case B200_ERR_CUDA: return "CUDA call failed";
+    case B200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    default: return "unknown status";
+  }
+}
+
+int b200_gemm_last_cuda_error(void) { return g_last_cuda_error; }
+
+int b200_gemm_sm_count(void) {
+  int dev = 0, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return -1;
+  }
+  return v;
+}
+
+}  // extern "C"

@@ -1,0 +1,402 @@
+// The one warp-specialised persistent GEMM kernel for sm_100a:  C[M,N] = A[M,K] * B[N,K]^T,
+// 16-bit inputs, fp32 accumulation in tensor memory, bf16 output.
+//
+// It takes the place of both reference kernels — gpu_gemm_kernel (matmul_h100.cu.jinja:734-925:
+// producer warpgroup + two ping-pong WGMMA consumer warpgroups) and matmulKernel
+// (matmul_utils.cuh:380-566: producer + two cooperative consumers) — with a Blackwell design:
+//
+//   warp 0      TMA producer   one lane streams A/B K-tiles into a shared-memory ring
+//   warp 1      MMA issuer     one lane issues tcgen05.mma; owns tensor-memory alloc/dealloc
+//   warps 2-5   epilogue       tcgen05.ld -> bf16 -> swizzled smem -> TMA store (one slab/warp)
+//
+// Barriers (all mbarriers in shared memory, every wait bounded):
+//   full[s]       TMA bytes of stage s have landed           (producer -> MMA issuer)
+//   empty[s]      MMAs reading stage s have completed        (tcgen05.commit -> producer)
+//   tmem_full[a]  accumulator buffer a holds a finished tile (tcgen05.commit -> epilogue)
+//   tmem_empty[a] accumulator buffer a has been read out     (epilogue -> MMA issuer)
+// Two accumulator buffers in tensor memory let the epilogue of one tile overlap the main loop of
+// the next; this replaces the reference's two consumer warpgroups and its OrderedBarrier
+// (matmul_h100.cu.jinja:61-113).
+//
+// PAIR = 1 runs a CTA pair (cluster of 2 along M) as one worker: tcgen05.mma.cta_group::2 computes
+// a 256 x BN tile, each CTA stages its own 128 rows of A and BN/2 rows of B with plain (unicast)
+// TMA loads that complete on the leader CTA's full[s]; the leader alone issues MMAs and signals
+// empty[s] / tmem_full[a] in both CTAs with one commit.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "desc.cuh"
+#include "ptx.cuh"
+#include "scheduler.cuh"
+
+namespace b200 {
+
+static constexpr int kBlockK = 64;          // one 128-byte swizzle row of 16-bit elements
+static constexpr int kUmmaK = 16;           // K of one tcgen05.mma (16-bit inputs)
+static constexpr int kCtaRows = 128;        // accumulator rows (TMEM lanes) per CTA
+static constexpr int kNumThreads = 192;     // 6 warps
+static constexpr int kEpiWarps = 4;
+static constexpr int kAccStages = 2;
+static constexpr int kMaxStages = 12;
+static constexpr int kEpiChunkCols = 64;    // columns per TMA store (128 bytes of bf16)
+static constexpr int kEpiSlabBytes = 32 * kEpiChunkCols * 2;       // one warp, one buffer: 4 KB
+static constexpr int kEpiBytes = kEpiWarps * 2 * kEpiSlabBytes;    // 32 KB
+static constexpr int kBarrierBytes = 256;
+
+// Device status codes written to the status word when a bounded wait gives up.
+enum DeviceStatus : unsigned int {
+  kStatusOk = 0,
+  kStatusProducerTimeout = 1,   // producer waited for empty[s]
+  kStatusMmaFullTimeout = 2,    // MMA issuer waited for full[s]
+  kStatusMmaTmemTimeout = 3,    // MMA issuer waited for tmem_empty[a]
+  kStatusEpilogueTimeout = 4,   // epilogue waited for tmem_full[a]
+};
+
+struct GemmArgs {
+  int M, N, K, batch;
+  SchedParams sched;
+  int stages;
+  int c_direct;               // 1: write C with predicated global stores instead of TMA
+  __nv_bfloat16* C;           // used when c_direct
+  long long ldc;              // elements between rows of C
+  long long c_batch_stride;   // elements between batches of C
+  float* partial;             // fp32 slots for split-K / stream-K partial tiles
+  float alpha, beta;
+  int scale;                  // 1: C = acc * alpha + beta (the scalar-beta rule of reference.h:40)
+  unsigned int* status;       // 4 words: code, block, tile, detail
+};
+
+template <int BN, int PAIR>
+struct KernelTraits {
+  static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN must be 64, 128, 192 or 256");
+  static constexpr int kCtaGroup = PAIR ? 2 : 1;
+  static constexpr int kBlockM = kCtaRows * kCtaGroup;
+  static constexpr int kBRowsCta = BN / kCtaGroup;
+  static constexpr int kABytes = kCtaRows * kBlockK * 2;
+  static constexpr int kBBytes = kBRowsCta * kBlockK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = (kAccStages * BN <= 32)    ? 32
+                                   : (kAccStages * BN <= 64)  ? 64
+                                   : (kAccStages * BN <= 128) ? 128
+                                   : (kAccStages * BN <= 256) ? 256
+                                                              : 512;
+  static constexpr uint32_t kIdescBf16 = make_instr_desc(kBlockM, BN, InFormat::BF16);
+  static constexpr uint32_t kIdescF16 = make_instr_desc(kBlockM, BN, InFormat::F16);
+  static constexpr int smem_bytes(int stages) {
+    return 1024 + stages * kStageBytes + kEpiBytes + kBarrierBytes;
+  }
+  static constexpr int max_stages() {
+    int s = (232448 - 1024 - kEpiBytes - kBarrierBytes) / kStageBytes;
+    return s > kMaxStages ? kMaxStages : s;
+  }
+};
+
+__device__ __forceinline__ void report_timeout(const GemmArgs& args, unsigned int code, int tile,
+                                               int detail, volatile uint32_t* abort_flag) {
+  if (atomicCAS(args.status, 0u, code) == 0u) {
+    args.status[1] = blockIdx.x;
+    args.status[2] = static_cast<unsigned int>(tile);
+    args.status[3] = static_cast<unsigned int>(detail);
+  }
+  *abort_flag = 1u;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int BN, int PAIR>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmArgs args) {
+  using T = KernelTraits<BN, PAIR>;
+  constexpr int G = T::kCtaGroup;
+  extern __shared__ uint8_t smem_raw[];
+
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x) / 32, 0);
+  const uint32_t lane = ptx::lane_id();
+  const uint32_t cta_rank = PAIR ? ptx::cluster_ctarank() : 0u;
+  const int worker = PAIR ? static_cast<int>(ptx::cluster_id_x()) : static_cast<int>(blockIdx.x);
+
+  const int stages = args.stages;
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t epi_base = smem_base + static_cast<uint32_t>(stages) * T::kStageBytes;
+  const uint32_t bar_base = epi_base + kEpiBytes;
+  auto a_addr = [&](int s) { return smem_base + static_cast<uint32_t>(s) * T::kStageBytes; };
+  auto b_addr = [&](int s) { return a_addr(s) + T::kABytes; };
+  auto full_bar = [&](int s) { return bar_base + 8u * static_cast<uint32_t>(s); };
+  auto empty_bar = [&](int s) { return bar_base + 8u * static_cast<uint32_t>(kMaxStages + s); };
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * static_cast<uint32_t>(2 * kMaxStages + a); };
+  auto tmem_empty_bar = [&](int a) {
+    return bar_base + 8u * static_cast<uint32_t>(2 * kMaxStages + kAccStages + a);
+  };
+  const uint32_t tmem_ptr_addr = bar_base + 8u * (2 * kMaxStages + 2 * kAccStages);
+  uint8_t* generic_bar = smem_raw + (bar_base - ptx::smem_u32(smem_raw));
+  volatile uint32_t* tmem_ptr_slot =
+      reinterpret_cast<volatile uint32_t*>(generic_bar + 8 * (2 * kMaxStages + 2 * kAccStages));
+  volatile uint32_t* abort_flag = tmem_ptr_slot + 1;
+
+  // ---------------------------------------------------------------- set-up
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+    ptx::prefetch_tensormap(&map_c);
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < kAccStages; ++a) {
+      ptx::mbar_init(tmem_full_bar(a), 1);
+      ptx::mbar_init(tmem_empty_bar(a), kEpiWarps * G);
+    }
+    *abort_flag = 0u;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<G>(tmem_ptr_addr, T::kTmemCols);
+    ptx::tmem_relinquish<G>();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (PAIR) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  // ---------------------------------------------------------------- roles
+  if (warp == 0) {
+    // ===== TMA producer =====
+    if (lane == 0) {
+      const uint32_t full_base_leader = PAIR ? ptx::map_to_cta(full_bar(0), 0) : full_bar(0);
+      WorkIter it(args.sched, worker);
+      Segment seg;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      while (ok && it.next(seg)) {
+        const TileCoord tc = tile_coord(args.sched, seg.tile);
+        const int row_a = tc.m * T::kBlockM + static_cast<int>(cta_rank) * kCtaRows;
+        const int row_b = tc.n * BN + static_cast<int>(cta_rank) * T::kBRowsCta;
+        for (int kt = seg.k_begin; kt < seg.k_end; ++kt) {
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u)) {
+            report_timeout(args, kStatusProducerTimeout, seg.tile, kt, abort_flag);
+            ok = false;
+            break;
+          }
+          if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), T::kStageBytes * G);
+          if (PAIR) {
+            const uint32_t bar = full_base_leader + 8u * static_cast<uint32_t>(stage);
+            ptx::tma_load_3d_pair(a_addr(stage), &map_a, bar, kt * kBlockK, row_a, tc.b);
+            ptx::tma_load_3d_pair(b_addr(stage), &map_b, bar, kt * kBlockK, row_b, tc.b);
+          } else {
+            ptx::tma_load_3d(a_addr(stage), &map_a, full_bar(stage), kt * kBlockK, row_a, tc.b);
+            ptx::tma_load_3d(b_addr(stage), &map_b, full_bar(stage), kt * kBlockK, row_b, tc.b);
+          }
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ===== MMA issuer (leader CTA only) =====
+    if (lane == 0 && cta_rank == 0) {
+      WorkIter it(args.sched, worker);
+      Segment seg;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      while (ok && it.next(seg)) {
+        if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u)) {
+          report_timeout(args, kStatusMmaTmemTimeout, seg.tile, acc, abort_flag);
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kt = seg.k_begin; kt < seg.k_end; ++kt) {
+          if (!ptx::mbar_wait(full_bar(stage), phase)) {
+            report_timeout(args, kStatusMmaFullTimeout, seg.tile, kt, abort_flag);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint64_t desc_a = make_smem_desc_sw128(a_addr(stage));
+          const uint64_t desc_b = make_smem_desc_sw128(b_addr(stage));
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            ptx::umma_f16<G>(tmem_d, desc_a + k * kDescKStep, desc_b + k * kDescKStep,
+                             T::kIdescBf16, (kt > seg.k_begin || k > 0) ? 1u : 0u);
+          }
+          if (PAIR) {
+            ptx::umma_commit_pair(empty_bar(stage), 3);
+          } else {
+            ptx::umma_commit_1cta(empty_bar(stage));
+          }
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        if (PAIR) {
+          ptx::umma_commit_pair(tmem_full_bar(acc), 3);
+        } else {
+          ptx::umma_commit_1cta(tmem_full_bar(acc));
+        }
+        if (++acc == kAccStages) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ===== epilogue warps =====
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const uint32_t slab0 = epi_base + static_cast<uint32_t>(warp - 2) * (2 * kEpiSlabBytes);
+    const uint32_t tmem_empty_leader =
+        PAIR ? ptx::map_to_cta(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+    WorkIter it(args.sched, worker);
+    Segment seg;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    uint32_t store_count = 0;
+    while (it.next(seg)) {
+      if (!ptx::mbar_wait(tmem_full_bar(acc), acc_phase)) {
+        if (lane == 0) report_timeout(args, kStatusEpilogueTimeout, seg.tile, acc, abort_flag);
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const TileCoord tc = tile_coord(args.sched, seg.tile);
+      const int tile_row = static_cast<int>(cta_rank) * kCtaRows + q * 32;  // slab row in tile
+      const int m_slab = tc.m * T::kBlockM + tile_row;
+      const int n_tile = tc.n * BN;
+      const uint32_t tmem_acc =
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      const bool to_slot = seg.slot >= 0;
+      const bool rows_live = to_slot || (m_slab < args.M);
+
+#pragma unroll 1
+      for (int c = 0; c < BN / kEpiChunkCols; ++c) {
+        const int n0 = n_tile + c * kEpiChunkCols;
+        const bool live = rows_live && (to_slot || n0 < args.N);
+        uint32_t v[2][32];
+        if (live) {
+          ptx::tmem_ld_32x32b_x32(tmem_acc + static_cast<uint32_t>(c * kEpiChunkCols), v[0]);
+          ptx::tmem_ld_32x32b_x32(tmem_acc + static_cast<uint32_t>(c * kEpiChunkCols + 32), v[1]);
+          ptx::tmem_ld_wait();
+        }
+        if (c == BN / kEpiChunkCols - 1) {
+          // All reads of this accumulator buffer are done: hand it back to the MMA issuer.
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::mbar_arrive_cluster(tmem_empty_leader + 8u * static_cast<uint32_t>(acc));
+          }
+        }
+        if (!live) continue;
+
+        if (to_slot) {
+          // fp32 partial tile: slot[row][col], row-major, tile-local coordinates.
+          float* dst = args.partial +
+                       (static_cast<long long>(seg.slot) * T::kBlockM + tile_row + lane) * BN +
+                       c * kEpiChunkCols;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 f = make_float4(__uint_as_float(v[h][j]), __uint_as_float(v[h][j + 1]),
+                                     __uint_as_float(v[h][j + 2]), __uint_as_float(v[h][j + 3]));
+              *reinterpret_cast<float4*>(dst + h * 32 + j) = f;
+            }
+          }
+          continue;
+        }
+
+        if (args.scale) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              v[h][j] = __float_as_uint(
+                  __fadd_rn(__fmul_rn(__uint_as_float(v[h][j]), args.alpha), args.beta));
+            }
+          }
+        }
+
+        if (args.c_direct) {
+          const int m = m_slab + static_cast<int>(lane);
+          if (m < args.M) {
+            __nv_bfloat16* dst = args.C + tc.b * args.c_batch_stride + m * args.ldc + n0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (n0 + h * 32 + j < args.N) dst[h * 32 + j] = __float2bfloat16_rn(__uint_as_float(v[h][j]));
+              }
+            }
+          }
+          continue;
+        }
+
+        // bf16 -> swizzled staging slab -> TMA store of a 32-row x 64-column box.
+        const uint32_t slab = slab0 + (store_count & 1u) * kEpiSlabBytes;
+        if (lane == 0) ptx::tma_store_wait_read<1>();  // the slab used two stores ago is free
+        __syncwarp();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t chunk = static_cast<uint32_t>(h * 4 + j);
+            ptx::st_shared_v4(
+                slab + sw128_offset(lane, chunk),
+                pack_bf16(__uint_as_float(v[h][8 * j + 0]), __uint_as_float(v[h][8 * j + 1])),
+                pack_bf16(__uint_as_float(v[h][8 * j + 2]), __uint_as_float(v[h][8 * j + 3])),
+                pack_bf16(__uint_as_float(v[h][8 * j + 4]), __uint_as_float(v[h][8 * j + 5])),
+                pack_bf16(__uint_as_float(v[h][8 * j + 6]), __uint_as_float(v[h][8 * j + 7])));
+          }
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::tma_store_3d(&map_c, slab, n0, m_slab, tc.b);
+          ptx::tma_store_commit();
+        }
+        ++store_count;
+      }
+      if (++acc == kAccStages) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+    if (lane == 0) ptx::tma_store_wait<0>();
+    __syncwarp();
+  }
+
+  // ---------------------------------------------------------------- teardown
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0u) {
+    // A wait gave up: give this CTA's outstanding bulk copies time to land before its shared
+    // memory and tensor memory are released.
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  if (PAIR) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc<G>(tmem_base, T::kTmemCols);
+  }
+}
+
+}  // namespace b200

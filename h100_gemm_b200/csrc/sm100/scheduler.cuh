@@ -1,0 +1,184 @@
+// Persistent tile scheduler: which (tile, K-range) segments each worker (a CTA, or a CTA pair)
+// processes, and in which order tiles are rasterised over the output.
+//
+// Replaces the reference's static along-N TileScheduler (matmul_h100.cu.jinja:392-439) and the
+// 16x8 supertile Schedule (matmul_utils.cuh:348-378). Three decompositions share one iterator:
+//   mode 0  data-parallel : worker w takes tiles w, w+W, w+2W, ... over the full K range
+//   mode 1  split-K       : every tile is cut into `split_k` K-slices; partial sums go to slots
+//   mode 2  stream-K      : the tiles x k_tiles iteration space is cut into W equal contiguous
+//                           ranges; a range's first/last tile may be partial
+// Partial segments carry a slot index into an fp32 workspace; a fix-up pass sums the slots of a
+// tile in a fixed order, so results do not depend on timing.
+//
+// Everything here compiles for the host as well, so coverage (every (tile, k) iteration visited
+// exactly once) is tested exhaustively without a GPU.
+#pragma once
+
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define B200_SCHED_HD __host__ __device__ __forceinline__
+#else
+#define B200_SCHED_HD inline
+#endif
+
+namespace b200 {
+
+enum SchedMode : int { kDataParallel = 0, kSplitK = 1, kStreamK = 2 };
+
+struct SchedParams {
+  int tiles_m;      // output tiles along M
+  int tiles_n;      // output tiles along N
+  int batch;        // independent problems
+  int num_tiles;    // tiles_m * tiles_n * batch
+  int k_tiles;      // K-tiles (of 64 elements) per output tile
+  int group;        // raster group width in tiles (>= 1)
+  int raster;       // 0: groups of `group` M-tiles, walked M-fastest; 1: same along N
+  int mode;         // SchedMode
+  int split_k;      // K-slices per tile (mode 1)
+  int num_workers;  // CTAs (or CTA pairs) in the grid
+};
+
+struct TileCoord {
+  int m;  // tile index along M
+  int n;  // tile index along N
+  int b;  // batch index
+};
+
+struct Segment {
+  int tile;     // linear tile id
+  int k_begin;  // first K-tile (inclusive)
+  int k_end;    // last K-tile (exclusive)
+  int slot;     // < 0: this segment produces the final output; >= 0: fp32 partial slot index
+};
+
+// Linear tile id -> coordinates. Inside a batch, tiles are grouped into bands of `group` tiles
+// along the grouped dimension and walked fastest along it, so that the tiles in flight at one
+// time (consecutive ids) form a compact block of the output and share operand panels in L2.
+B200_SCHED_HD TileCoord tile_coord(const SchedParams& p, int tile) {
+  TileCoord c;
+  const int per_batch = p.tiles_m * p.tiles_n;
+  c.b = tile / per_batch;
+  int t = tile - c.b * per_batch;
+  const int major = p.raster == 0 ? p.tiles_m : p.tiles_n;  // grouped dimension
+  const int minor = p.raster == 0 ? p.tiles_n : p.tiles_m;
+  const int band_size = p.group * minor;
+  const int band = t / band_size;
+  const int first = band * p.group;
+  const int width = (major - first) < p.group ? (major - first) : p.group;
+  const int r = t - band * band_size;
+  const int a = first + r % width;
+  const int o = r / width;
+  c.m = p.raster == 0 ? a : o;
+  c.n = p.raster == 0 ? o : a;
+  return c;
+}
+
+B200_SCHED_HD long long sched_total_iters(const SchedParams& p) {
+  return static_cast<long long>(p.num_tiles) * p.k_tiles;
+}
+
+// First iteration of worker w's contiguous stream-K range.
+B200_SCHED_HD long long streamk_begin(const SchedParams& p, int w) {
+  return sched_total_iters(p) * w / p.num_workers;
+}
+
+// K-range of slice s under split-K.
+B200_SCHED_HD int splitk_begin(const SchedParams& p, int s) {
+  return static_cast<int>(static_cast<long long>(p.k_tiles) * s / p.split_k);
+}
+
+// Number of fp32 partial slots the workspace must hold.
+B200_SCHED_HD long long sched_num_slots(const SchedParams& p) {
+  if (p.mode == kSplitK) return p.split_k > 1 ? static_cast<long long>(p.split_k) * p.num_tiles : 0;
+  if (p.mode == kStreamK) return 2ll * p.num_workers;
+  return 0;
+}
+
+// Iterates over the segments of one worker. All roles of a CTA (producer, MMA issuer, epilogue)
+// run their own copy and therefore agree on the sequence without communicating.
+struct WorkIter {
+  const SchedParams& p;
+  int worker;
+  long long cur;  // mode 0/1: next unit id; mode 2: next iteration
+  long long end;  // mode 2: end of this worker's range
+  long long range_begin;
+
+  B200_SCHED_HD WorkIter(const SchedParams& params, int w) : p(params), worker(w) {
+    if (p.mode == kStreamK) {
+      cur = streamk_begin(p, w);
+      end = streamk_begin(p, w + 1);
+      range_begin = cur;
+    } else {
+      cur = w;
+      end = static_cast<long long>(p.num_tiles) * (p.mode == kSplitK ? p.split_k : 1);
+      range_begin = 0;
+    }
+  }
+
+  B200_SCHED_HD bool next(Segment& s) {
+    if (cur >= end) return false;
+    if (p.mode == kDataParallel) {
+      s.tile = static_cast<int>(cur);
+      s.k_begin = 0;
+      s.k_end = p.k_tiles;
+      s.slot = -1;
+      cur += p.num_workers;
+    } else if (p.mode == kSplitK) {
+      const int slice = static_cast<int>(cur / p.num_tiles);
+      s.tile = static_cast<int>(cur - static_cast<long long>(slice) * p.num_tiles);
+      s.k_begin = splitk_begin(p, slice);
+      s.k_end = splitk_begin(p, slice + 1);
+      s.slot = p.split_k > 1 ? slice * p.num_tiles + s.tile : -1;
+      cur += p.num_workers;
+    } else {
+      s.tile = static_cast<int>(cur / p.k_tiles);
+      const long long tile_first = static_cast<long long>(s.tile) * p.k_tiles;
+      s.k_begin = static_cast<int>(cur - tile_first);
+      long long stop = tile_first + p.k_tiles;
+      if (stop > end) stop = end;
+      s.k_end = static_cast<int>(stop - tile_first);
+      const bool full = (s.k_begin == 0) && (s.k_end == p.k_tiles);
+      s.slot = full ? -1 : 2 * worker + (cur == range_begin ? 0 : 1);
+      cur = stop;
+    }
+    return true;
+  }
+};
+
+// For the fix-up pass: the slots that hold partial sums of `tile`, in summation order.
+// Returns the count (0 when the tile was produced whole); writes at most `cap` slot ids.
+B200_SCHED_HD int tile_partial_slots(const SchedParams& p, int tile, int* slots, int cap) {
+  int n = 0;
+  if (p.mode == kSplitK) {
+    if (p.split_k <= 1) return 0;
+    for (int s = 0; s < p.split_k; ++s) {
+      if (splitk_begin(p, s + 1) == splitk_begin(p, s)) continue;  // empty slice
+      if (n < cap) slots[n] = s * p.num_tiles + tile;
+      ++n;
+    }
+    return n;
+  }
+  if (p.mode != kStreamK) return 0;
+  const long long first = static_cast<long long>(tile) * p.k_tiles;
+  const long long last = first + p.k_tiles;
+  const long long total = sched_total_iters(p);
+  // Worker that owns iteration `first`: largest w with streamk_begin(w) <= first.
+  int w = static_cast<int>((first * p.num_workers) / total);
+  while (w + 1 < p.num_workers && streamk_begin(p, w + 1) <= first) ++w;
+  while (w > 0 && streamk_begin(p, w) > first) --w;
+  for (; w < p.num_workers; ++w) {
+    const long long rb = streamk_begin(p, w);
+    const long long re = streamk_begin(p, w + 1);
+    if (rb >= last) break;
+    if (re <= first || re == rb) continue;
+    const long long sb = rb > first ? rb : first;
+    const long long se = re < last ? re : last;
+    if (sb == first && se == last) return 0;  // one worker produced the whole tile
+    if (n < cap) slots[n] = 2 * w + (sb == rb ? 0 : 1);
+    ++n;
+  }
+  return n;
+}
+
+}  // namespace b200

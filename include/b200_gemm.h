@@ -1,0 +1,131 @@
+/* C ABI of the B200 (sm_100a) dense GEMM:  C[M,N] = A[M,K] * B[N,K]^T, bf16 in, fp32 accumulate,
+ * bf16 out. A and B are both K-contiguous ("K-major"); C is row-major unless stated otherwise.
+ *
+ * This header is the drop-in boundary for the host launchers of Faraz9877/H100_GEMM. Each entry
+ * point names the reference interface it replaces (paths are relative to that project).
+ * Plain pointers and sizes only; no C++ or framework types. Every function returns a
+ * b200_status code (0 = success) instead of calling exit()/assert() as the reference does
+ * (common.h:29-37, tma.cuh:95-178). Nothing here falls back to a CPU implementation: without a
+ * CUDA device the compute entry points return B200_ERR_CUDA.
+ *
+ * All pointers are device pointers unless the parameter name starts with `h`.
+ * `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream, as the
+ * reference launches on, matmul_h100.cu.jinja:970).
+ */
+#ifndef B200_GEMM_H_
+#define B200_GEMM_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum b200_status {
+  B200_OK = 0,
+  B200_ERR_INVALID_ARG = 1,     /* NULL pointer, non-positive size, bad enum value          */
+  B200_ERR_UNSUPPORTED_CFG = 2, /* tile/cluster/stage combination that has no kernel        */
+  B200_ERR_SMEM = 3,            /* configuration needs more shared memory than an SM has    */
+  B200_ERR_WORKSPACE = 4,       /* workspace missing or smaller than b200_gemm_workspace_bytes */
+  B200_ERR_CUDA = 5,            /* a CUDA runtime/driver call failed (see b200_gemm_last_cuda_error) */
+  B200_ERR_DEVICE_TIMEOUT = 6,  /* a bounded wait inside the kernel gave up                 */
+  B200_ERR_ALPHA_BETA = 7       /* reserved                                                 */
+} b200_status;
+
+/* Tunable surface. The first six fields are the template variables of the reference's
+ * matmul_h100.cu.jinja:9-14 / gemm_tuner.py:17-24 and keep their meaning:
+ *   block_m   rows of C per CTA. 128 (one tcgen05 accumulator of 128 TMEM lanes).
+ *   block_n   columns of C per tile: 64, 128, 192 or 256.
+ *   block_k   K-tile staged per pipeline stage: 64 (one 128-byte swizzle row).
+ *   stages    shared-memory ring depth; 0 = as many as fit.
+ *   cluster_m CTAs along M that share one B tile. 1 = single-CTA MMA. 2 = a CTA pair driving one
+ *             tcgen05.mma.cta_group::2 (256 x block_n per pair; each CTA stages half of B). Larger
+ *             powers of two keep the pair and only widen the raster group (no multicast loads).
+ *   cluster_n must be 1 (the reference's tuner rejects anything else, gemm_tuner.py:77-78).
+ * The rest are additions with neutral defaults (all zero):
+ *   sched     0 data-parallel tiles, 1 split-K, 2 stream-K.
+ *   split_k   K-slices per tile for sched 1 (0/1 = none).
+ *   raster    0 group tiles along M, 1 along N.
+ *   group     raster group width in tiles; 0 = default (8).
+ *   c_col_major  0: C row-major [M,N] (matmul_h100.cu.jinja:696); 1: column-major, leading
+ *             dimension M (matmul_utils.cuh:529,545).
+ *   max_ctas  cap on the persistent grid; 0 = every SM.
+ */
+typedef struct b200_gemm_cfg {
+  int block_m;
+  int block_n;
+  int block_k;
+  int stages;
+  int cluster_m;
+  int cluster_n;
+  int sched;
+  int split_k;
+  int raster;
+  int group;
+  int c_col_major;
+  int max_ctas;
+} b200_gemm_cfg;
+
+/* Replaces gpu_gemm<AType,BType,CType,AccumType,CLUSTER_M,CLUSTER_N,BLOCKM,BLOCKN,BLOCKK,STAGES>
+ * (GemmParams) — matmul_h100.cu.jinja:927-985 — for bf16. cfg == NULL picks a configuration from
+ * the shape. The result is (bf16)(acc * alpha + beta): beta is added as a SCALAR, which is what
+ * the reference's own GEMMs define (reference.h:40,72); alpha = 1, beta = 0 is the fast path the
+ * reference's kernels hard-wire (matmul_h100.cu.jinja:696).
+ * `workspace` may be NULL when b200_gemm_workspace_bytes() returns 0 for the same arguments.
+ * Asynchronous on `stream`; no host synchronisation, no allocation. */
+int b200_gemm_bf16(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
+                   float beta, const b200_gemm_cfg* cfg, void* workspace, size_t workspace_bytes,
+                   void* stream);
+
+/* `batch` independent GEMMs of one shape; stride* are element distances between consecutive
+ * problems. No counterpart function in the reference; it covers the batched configuration its
+ * rank-3 tensor maps are built for (tma.cuh:83-181 with TmaDim = 3). */
+int b200_gemm_batched_bf16(int batch, int M, int N, int K, const void* A, long long strideA,
+                           const void* B, long long strideB, void* C, long long strideC,
+                           float alpha, float beta, const b200_gemm_cfg* cfg, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
+/* Bytes of device workspace the two functions above need for these arguments: fp32 partial
+ * tiles for split-K / stream-K, and re-pitched copies of A and B when K is not a multiple of 8
+ * elements (TMA needs a 16-byte row pitch — the reference asserts it, tma.cuh:109). */
+size_t b200_gemm_workspace_bytes(int batch, int M, int N, int K, const b200_gemm_cfg* cfg);
+
+/* Fills *cfg with the configuration cfg == NULL would use for this shape. */
+int b200_gemm_default_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg);
+
+/* Replaces runKernel(int M,int N,int K,bf16* A,bf16* B,bf16* C,int* DB) —
+ * matmul_h100_optimal.cu:32-59: default configuration, COLUMN-major C (ld = M), default stream.
+ * DB is accepted and ignored, as in the reference (matmul_h100_optimal.cu:32,58). */
+int b200_run_kernel(int M, int N, int K, void* A, void* B, void* C, int* DB);
+
+/* Same GEMM with HOST buffers (pageable or pinned): copies A and B to the device in row bands,
+ * overlapping the copies with the kernel, and copies C back. Synchronous. It keeps device
+ * staging buffers between calls (released by b200_gemm_host_release). This is the call a
+ * harness like the reference's main() makes around its copy_to_gpu / gpu_gemm / copy_to_cpu
+ * sequence (matmul_h100.cu.jinja:1036-1054). */
+int b200_gemm_bf16_host(int M, int N, int K, const void* hA, const void* hB, void* hC, float alpha,
+                        float beta, const b200_gemm_cfg* cfg);
+void b200_gemm_host_release(void);
+
+/* Replaces reference_gpu_gemm(GemmParams) — reference.h:49-90: a plain SIMT GEMM (one thread per
+ * 4x4 outputs, k ascending, fp32) used as an on-device cross-check for shapes too large for the
+ * CPU oracle. */
+int b200_reference_gpu_gemm_bf16(int M, int N, int K, const void* A, const void* B, void* C,
+                                 float alpha, float beta, void* stream);
+
+/* Synchronises the current device and reports the device-side status word: out[0] = 0 when no
+ * bounded wait has given up since the last call; otherwise out[0] = role code, out[1] = block,
+ * out[2] = tile, out[3] = detail. Returns B200_OK or B200_ERR_DEVICE_TIMEOUT; the word is
+ * cleared. (The reference's waits are unbounded, barrier.cuh:47-62.) */
+int b200_gemm_last_device_status(unsigned int out[4]);
+
+const char* b200_gemm_strerror(int status);
+/* cudaError_t / CUresult value of the most recent failing CUDA call on this thread. */
+int b200_gemm_last_cuda_error(void);
+/* Multiprocessor count of the current device (get_sm_count, common.h:43-60); <= 0 on error. */
+int b200_gemm_sm_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_GEMM_H_ */
