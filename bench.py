@@ -1,0 +1,380 @@
+#!/usr/bin/env python
+"""Headline benchmark: bf16 GEMM C = A * B^T (fp32 accumulate, bf16 out) in TFLOP/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One step = one pass of the hot path over one synthetic problem:
+  * N = 1: M = N = K = 8192, uniform[-1,1] bf16 inputs (the configuration the headline metric is
+    quoted on). Inputs (3 x 134 MB) exceed L2 (126 MB), so no L2 flush between steps.
+  * N > 1 (one process per GPU, launched by torch.distributed.run): the M-sharded prefill GEMM,
+    8192 rows of A ~ N(0,1) per rank, B ~ N(0,0.02) replicated, no data-path collective
+    (65536 x 8192 x 8192 at N = 8). Weak scaling: per-GPU work is fixed.
+`value` is device-resident throughput (CUDA events on the launching stream, max over ranks);
+`e2e` is the same metric through the host-buffer C-ABI call with pinned host inputs and outputs,
+copies inside the timed region. `--impl reference` times the reference project's own CPU GEMM
+(reference.h compiled in place into oracle/_ref; else the C restatement) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+WORKLOADS = {
+    # name: (M per rank, N, K, generator of A, generator of B)
+    "square8192": (8192, 8192, 8192, "uniform", "uniform"),
+    "square4096": (4096, 4096, 4096, "uniform", "uniform"),
+    "square16384": (16384, 16384, 16384, "uniform", "uniform"),
+    "prefill_shard": (8192, 8192, 8192, "normal", "normal0.02"),
+    "skinny16": (16, 28672, 8192, "normal", "normal0.02"),
+    "skinny32": (32, 28672, 8192, "normal", "normal0.02"),
+    "skinny64": (64, 28672, 8192, "normal", "normal0.02"),
+    "skinny128": (128, 28672, 8192, "normal", "normal0.02"),
+}
+HBM_BOUND = {"skinny16", "skinny32", "skinny64", "skinny128"}
+
+# DRAM bytes (read + write) of one gemm_kernel launch at 8192^3, from the ncu capture summarised in
+# profiles/gemm_kernel_8192.md; None until a capture of the current kernel exists.
+NCU_DRAM_BYTES_PER_LAUNCH = {"square8192": None}
+
+
+def measured_peaks():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "burst": d["bf16_tflops"], "sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "burst": 1590.0, "sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    REASONS = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
+               0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
+               0x100: "display_clock_setting"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.002)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def physical_gpu_index(local_index: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except Exception:
+            return local_index
+    return local_index
+
+
+def make_inputs(torch, M, N, K, kind_a, kind_b, seed, device):
+    gen = torch.Generator(device=device)
+
+    def draw(shape, kind, s):
+        gen.manual_seed(s)
+        if kind == "uniform":
+            x = torch.rand(shape, device=device, generator=gen) * 2 - 1
+        elif kind == "normal":
+            x = torch.randn(shape, device=device, generator=gen)
+        else:
+            x = torch.randn(shape, device=device, generator=gen) * 0.02
+        return x.to(torch.bfloat16)
+
+    return draw((M, K), kind_a, seed), draw((N, K), kind_b, 1)
+
+
+# --------------------------------------------------------------------------------------------
+# CPU baseline (oracle/ is only ever the checker or the timed baseline, never the product path)
+# --------------------------------------------------------------------------------------------
+def cpu_sample(N, K, kind_a, kind_b, rows, cols):
+    import numpy as np
+    from oracle import oracle
+    rng = np.random.Generator(np.random.Philox(0))
+
+    def draw(shape, kind):
+        if kind == "uniform":
+            x = rng.uniform(-1, 1, size=shape)
+        elif kind == "normal":
+            x = rng.standard_normal(size=shape)
+        else:
+            x = rng.standard_normal(size=shape) * 0.02
+        return oracle.f32_to_bf16_bits(x.astype(np.float32))
+
+    return draw((rows, K), kind_a), draw((min(cols, N), K), kind_b)
+
+
+def cpu_gemm_fn():
+    from oracle import oracle
+    if oracle.have_reference():
+        return oracle.reference_cpu_gemm, "reference"
+    return oracle.cpu_gemm, "port"
+
+
+def time_cpu(fn, a, b, repeats=1):
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        fn(a, b)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
+def cpu_baseline(workload, hbm_bound):
+    M, N, K, ka, kb = WORKLOADS[workload]
+    cores = os.cpu_count() or 1
+    threads = int(os.environ.get("OMP_NUM_THREADS", cores))
+    # The reference parallelises over 64-row blocks only (reference.h:14), so give every thread
+    # one block; cap the columns so the sample stays within tens of seconds.
+    rows = min(M, 64 * threads)
+    cols = N if hbm_bound else min(N, 2048)
+    a, b = cpu_sample(N, K, ka, kb, rows, cols)
+    fn, kind = cpu_gemm_fn()
+    dt = time_cpu(fn, a, b)
+    flops = 2.0 * a.shape[0] * b.shape[0] * K
+    if hbm_bound:
+        value, unit = 2.0 * (a.size + b.size + a.shape[0] * b.shape[0]) / dt / 1e9, "GB/s"
+    else:
+        value, unit = flops / dt / 1e12, "TFLOP/s"
+    return {"value": value, "unit": unit, "cores": min(threads, (rows + 63) // 64) if kind == "reference" else threads,
+            "kind": kind,
+            "sample": f"C[0:{a.shape[0]}, 0:{b.shape[0]}] of the {M}x{N}x{K} problem (full K), one run, {dt:.2f} s"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    workload = args.workload or "square8192"
+    M, N, K, ka, kb = WORKLOADS[workload]
+    hbm = workload in HBM_BOUND
+    cores = os.cpu_count() or 1
+    threads = int(os.environ.get("OMP_NUM_THREADS", cores))
+    rows = min(M, 64 * threads)
+    cols = N if hbm else min(N, 1024)
+    a, b = cpu_sample(N, K, ka, kb, rows, cols)
+    fn, kind = cpu_gemm_fn()
+    for _ in range(args.warmup):
+        fn(a, b)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn(a, b)
+    dt = time.perf_counter() - t0
+    flops = 2.0 * a.shape[0] * b.shape[0] * K * args.steps
+    if hbm:
+        metric, unit = "bf16 GEMM achieved GB/s (algorithmic bytes)", "GB/s"
+        value = 2.0 * (a.size + b.size + a.shape[0] * b.shape[0]) * args.steps / dt / 1e9
+    else:
+        metric, unit = "bf16 GEMM TFLOP/s", "TFLOP/s"
+        value = flops / dt / 1e12
+    used = min(threads, (rows + 63) // 64) if kind == "reference" else threads
+    line = {
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{workload}: M={M} N={N} K={K} per GPU, C = A*B^T, bf16 in/out, fp32 accumulate",
+                   "l2": "CPU run"},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": used, "kind": kind,
+                         "sample": f"each step: C[0:{a.shape[0]}, 0:{b.shape[0]}] of the problem (full K) with "
+                                   f"reference_cpu_gemm (reference.h:5-46), {used} OpenMP threads"},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# --------------------------------------------------------------------------------------------
+# Our arm
+# --------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import h100_gemm_b200 as g
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the GEMM has no CPU fallback")
+    g.library()
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    workload = args.workload or ("square8192" if world == 1 else "prefill_shard")
+    M, N, K, ka, kb = WORKLOADS[workload]
+    hbm = workload in HBM_BOUND
+    a, b = make_inputs(torch, M, N, K, ka, kb, seed=100 + rank, device=device)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+    cfg = g.default_config(1, M, N, K)
+    ws_bytes = g.workspace_bytes(1, M, N, K, cfg)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=device)
+    # B buffers to rotate through for HBM-bound shapes, so the weight stream cannot live in L2.
+    rot = 1
+    bs = [b]
+    if hbm:
+        rot = 3
+        bs = [b] + [b.clone() for _ in range(rot - 1)]
+    stream = torch.cuda.current_stream()
+    launches_per_step = 1 + (1 if cfg.sched != 0 else 0)
+
+    def step(i):
+        g.gemm(a, bs[i % rot], out=c, cfg=cfg, workspace=ws, stream=stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        e0.record(stream)
+        for i in range(args.steps):
+            step(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+    ms_total = e0.elapsed_time(e1)
+    barrier()
+    rc, words = g.device_status()
+    if rc != 0:
+        raise SystemExit(f"device status {words}")
+    t = torch.tensor([ms_total], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+
+    # ---- end to end: pinned host buffers through the host-buffer C-ABI entry point ----
+    ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
+    hc = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(1, min(args.steps, 10))
+    for _ in range(2):
+        g.gemm_host(ha, hb, hc)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        g.gemm_host(ha, hb, hc)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    te = torch.tensor([e2e_s], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_s = float(te.item())
+
+    flops_step = 2.0 * M * N * K
+    bytes_step = 2.0 * (M * K + N * K + M * N)
+    peaks = measured_peaks()
+    if hbm:
+        metric, unit = "bf16 GEMM achieved GB/s (algorithmic bytes)", "GB/s"
+        value = world * bytes_step / (ms_step * 1e-3) / 1e9
+        e2e_value = world * bytes_step * e2e_steps / e2e_s / 1e9
+        achieved = bytes_step / (ms_step * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(workload),
+                "peak_source": f"{peaks['source']} copy bandwidth"}
+    else:
+        metric, unit = "bf16 GEMM TFLOP/s", "TFLOP/s"
+        value = world * flops_step / (ms_step * 1e-3) / 1e12
+        e2e_value = world * flops_step * e2e_steps / e2e_s / 1e12
+        achieved = flops_step / (ms_step * 1e-3) / 1e12
+        kind = "burst" if ms_total < 1000.0 else "sustained"
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peaks[kind], "unit": "TFLOP/s",
+                "frac": achieved / peaks[kind], "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(workload),
+                "peak_source": f"{peaks['source']} cuBLAS bf16 {kind} ({'timed region < 1 s' if kind == 'burst' else 'timed region >= 1 s'})",
+                "frac_of_nominal_2250": achieved / 2250.0}
+
+    if rank == 0:
+        line = {
+            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": f"{workload}: M={M} N={N} K={K} per GPU, C = A*B^T, bf16 in/out, fp32 accumulate",
+                       "global_M": M * world, "parallelism": f"M-sharded x{world}, B replicated, no collective",
+                       "l2": "inputs larger than L2 (no flush)" if not hbm else f"{rot} rotating B buffers, each larger than L2",
+                       "kernel_cfg": {k: getattr(cfg, k) for k in ("block_m", "block_n", "block_k", "stages", "cluster_m", "sched")}},
+            "roofline": roof,
+            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int((M * K + N * K) * 2),
+                    "d2h_bytes_per_step": int(M * N * 2), "steps": e2e_steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks.summary(),
+        }
+        if world == 1:
+            try:
+                line["cpu_baseline"] = cpu_baseline(workload, hbm)
+            except Exception as exc:  # the CPU leg must never hide the GPU result
+                line["cpu_baseline"] = {"error": str(exc)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    if args.steps < 1 or args.warmup < 0:
+        raise SystemExit("--steps must be >= 1 and --warmup >= 0")
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

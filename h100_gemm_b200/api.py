@@ -87,6 +87,8 @@ def library() -> ctypes.CDLL:
     lib.b200_reference_gpu_gemm_bf16.restype = ci
     lib.b200_gemm_last_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint * 4)]
     lib.b200_gemm_last_device_status.restype = ci
+    lib.b200_gemm_selftest_bounded_wait.argtypes = [ll]
+    lib.b200_gemm_selftest_bounded_wait.restype = ci
     lib.b200_gemm_strerror.argtypes = [ci]
     lib.b200_gemm_strerror.restype = ctypes.c_char_p
     lib.b200_gemm_last_cuda_error.argtypes = []
@@ -262,6 +264,11 @@ def gemm_host(a_bits, b_bits, out_bits=None, alpha: float = 1.0, beta: float = 0
     keep, p = _cfg_ptr(cfg)
     _check(library().b200_gemm_bf16_host(M, N, K, pa, pb, pc, alpha, beta, p))
     return out_bits
+
+
+def selftest_bounded_wait(budget_cycles: int = 1 << 20) -> None:
+    """Launches the kernel whose only wait is designed to run out (see include/b200_gemm.h)."""
+    _check(library().b200_gemm_selftest_bounded_wait(budget_cycles))
 
 
 def device_status():

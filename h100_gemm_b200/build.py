@@ -77,6 +77,18 @@ def build_baselines(force: bool = False) -> Path:
     return BASELINES_PATH
 
 
+def build_host_shim(force: bool = False) -> Path:
+    """g++ -> lib/libb200gemm_hostshim.so: scheduler/descriptor arithmetic for CPU-only tests."""
+    LIB_DIR.mkdir(exist_ok=True)
+    out = LIB_DIR / "libb200gemm_hostshim.so"
+    srcs = [CSRC / "host_shim.cpp", CSRC / "sm100" / "desc.cuh", CSRC / "sm100" / "scheduler.cuh"]
+    if not force and _newer(out, srcs):
+        return out
+    _run(["/usr/bin/g++", "-std=c++17", "-O2", "-x", "c++", "-shared", "-fPIC", "-o", str(out),
+          str(CSRC / "host_shim.cpp")])
+    return out
+
+
 def build_oracle() -> None:
     """The CPU checker used by tests and the benchmark's CPU leg (never by the library)."""
     oracle_dir = REPO_DIR / "oracle"
@@ -89,6 +101,7 @@ def build_oracle() -> None:
 def build_all(force: bool = False) -> None:
     build_library(force=force)
     build_baselines(force=force)
+    build_host_shim(force=force)
     build_oracle()
 
 

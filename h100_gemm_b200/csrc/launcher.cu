@@ -769,6 +769,17 @@ int b200_gemm_last_device_status(unsigned int out[4]) {
   return B200_OK;
 }
 
+int b200_gemm_selftest_bounded_wait(long long budget_cycles) {
+  if (budget_cycles <= 0 || budget_cycles > (1ll << 31)) return B200_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState* st = nullptr;
+  int rc = get_device_state(&st);
+  if (rc != B200_OK) return rc;
+  bounded_wait_selftest_kernel<<<1, 32>>>(st->status, budget_cycles);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
 const char* b200_gemm_strerror(int status) {
   switch (status) {
     case B200_OK: return "success";

@@ -51,6 +51,7 @@ enum DeviceStatus : unsigned int {
   kStatusMmaFullTimeout = 2,    // MMA issuer waited for full[s]
   kStatusMmaTmemTimeout = 3,    // MMA issuer waited for tmem_empty[a]
   kStatusEpilogueTimeout = 4,   // epilogue waited for tmem_full[a]
+  kStatusSelfTestTimeout = 9,   // the bounded-wait self-test (an mbarrier nothing arrives on)
 };
 
 struct GemmArgs {
@@ -100,6 +101,25 @@ __device__ __forceinline__ void report_timeout(const GemmArgs& args, unsigned in
     args.status[3] = static_cast<unsigned int>(detail);
   }
   *abort_flag = 1u;
+}
+
+// Failure-detection self-test: waits, with a short cycle budget, on an mbarrier that nothing
+// ever arrives on, and reports the give-up through the same status word the GEMM roles use.
+// The kernel returns normally; the context stays usable.
+__global__ void bounded_wait_selftest_kernel(unsigned int* status, long long budget_cycles) {
+  __shared__ __align__(8) unsigned long long bar;
+  if (threadIdx.x == 0) {
+    const uint32_t b = ptx::smem_u32(&bar);
+    ptx::mbar_init(b, 1);
+    ptx::fence_mbar_init();
+    if (!ptx::mbar_wait(b, 0, budget_cycles)) {
+      if (atomicCAS(status, 0u, static_cast<unsigned int>(kStatusSelfTestTimeout)) == 0u) {
+        status[1] = blockIdx.x;
+        status[2] = 0u;
+        status[3] = 0u;
+      }
+    }
+  }
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

@@ -107,7 +107,7 @@ B200_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 static constexpr long long kWaitBudgetCycles = 1ll << 28;
 
 // Bounded wait: true when the phase with `parity` completed, false when the budget ran out.
-B200_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity) {
+B200_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, long long budget = kWaitBudgetCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
@@ -115,7 +115,7 @@ B200_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
-    if (clock64() - t0 > kWaitBudgetCycles) return false;
+    if (clock64() - t0 > budget) return false;
   }
 }
 

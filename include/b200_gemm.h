@@ -119,6 +119,13 @@ int b200_reference_gpu_gemm_bf16(int M, int N, int K, const void* A, const void*
  * cleared. (The reference's waits are unbounded, barrier.cuh:47-62.) */
 int b200_gemm_last_device_status(unsigned int out[4]);
 
+/* Failure-detection self-test: launches a one-block kernel that waits, for at most
+ * `budget_cycles` SM cycles (<= 2^31), on an mbarrier nothing arrives on. The wait gives up, the
+ * kernel returns normally and b200_gemm_last_device_status() then reports out[0] == 9. No
+ * counterpart in the reference, whose waits cannot give up (barrier.cuh:47-62,
+ * matmul_utils.cuh:279-293). */
+int b200_gemm_selftest_bounded_wait(long long budget_cycles);
+
 const char* b200_gemm_strerror(int status);
 /* cudaError_t / CUresult value of the most recent failing CUDA call on this thread. */
 int b200_gemm_last_cuda_error(void);
