@@ -296,6 +296,30 @@ def run_ours(args):
     ms_total = float(t.item())
     ms_step = ms_total / args.steps
 
+    # ---- optional: the same step followed by an NCCL all-gather of C, chunked and overlapped ----
+    gathered = None
+    if world > 1 and args.allgather:
+        from h100_gemm_b200.sharding import ShardedGemm
+        full = torch.empty(M * world, N, dtype=torch.bfloat16, device=device)
+        comm_stream = torch.cuda.Stream(device=device)
+        sg = ShardedGemm(M * world, a, b, lambda ar, bb, out: g.gemm(ar, bb, out=out, workspace=ws, stream=stream))
+        for _ in range(max(3, args.warmup)):
+            sg.compute_and_gather(full, chunks=4, comm_stream=comm_stream)
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        for _ in range(args.steps):
+            sg.compute_and_gather(full, chunks=4, comm_stream=comm_stream)
+        g1.record(stream)
+        torch.cuda.synchronize()
+        tg = torch.tensor([g0.elapsed_time(g1)], dtype=torch.float64, device=device)
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        g_ms = float(tg.item()) / args.steps
+        gathered = {"value": world * 2.0 * M * N * K / (g_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": g_ms,
+                    "collective": "NCCL all_gather of C, 4 row chunks per shard overlapped with the next chunk's GEMM",
+                    "bytes_received_per_gpu": int((world - 1) * M * N * 2)}
+        del full
+
     # ---- end to end: pinned host buffers through the host-buffer C-ABI entry point ----
     e2e_steps = max(1, min(args.steps, 10))
     e2e_s = float("nan")
@@ -352,6 +376,8 @@ def run_ours(args):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary(),
         }
+        if gathered is not None:
+            line["with_allgather"] = gathered
         if args.kernel_only:
             line["e2e"] = None
         if world == 1 and not args.kernel_only:
@@ -372,6 +398,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--allgather", action="store_true",
+                    help="N > 1: also time the variant that all-gathers C over NCCL (reported separately)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for profiler captures)")
     args = ap.parse_args()

@@ -1,0 +1,101 @@
+// Vendor-library baselines for the comparison harnesses: cuBLAS (cublasGemmEx) and cuBLASLt
+// (heuristic top-1, 32 MiB workspace). These are REPORTED BASELINES, built into their own shared
+// object (libb200gemm_baselines.so); the product library never links or calls them.
+//
+// They stand in for runCublasGemmBF16 (matmul_h100_optimal.cu:63-73), the fp16 cublasGemmEx
+// benchmark (cublas_ref/spmm_test.cu:137-179) and the cuBLASLt snippet (cublaslt_matmul.cu:13-74),
+// with the layout mapping written out for the K-major operands this project uses:
+//
+//   row-major  C[M,N] = A[M,K] * B[N,K]^T
+//     == column-major C^T (N x M, ld N) = op_T(B viewed as K x N, ld K) * op_N(A viewed as K x M, ld K)
+//   column-major C (M x N, ld M)        = op_T(A viewed as K x M, ld K) * op_N(B viewed as K x N, ld K)
+//
+// (The reference passes lda = N and ldc = N, matmul_h100_optimal.cu:66-67, which is only right
+// for M = N = K; its cuBLASLt snippet assumes column-major A and does not compile.)
+#include <cublasLt.h>
+#include <cublas_v2.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+
+namespace {
+cublasHandle_t g_cublas = nullptr;
+cublasLtHandle_t g_lt = nullptr;
+void* g_lt_workspace = nullptr;
+constexpr size_t kLtWorkspaceBytes = 32u << 20;  // cublaslt_matmul.cu:4
+int g_last_status = 0;
+}  // namespace
+
+extern "C" {
+
+int b200_baseline_last_status(void) { return g_last_status; }
+
+// c_col_major = 0: row-major C[M,N]; 1: column-major C (ld M), as the reference's cuBLAS call writes.
+int b200_baseline_cublas_gemm_bf16(int M, int N, int K, const void* A, const void* B, void* C,
+                                   int c_col_major, void* stream) {
+  if (g_cublas == nullptr) {
+    cublasStatus_t s = cublasCreate(&g_cublas);
+    if (s != CUBLAS_STATUS_SUCCESS) {
+      g_last_status = static_cast<int>(s);
+      return 1;
+    }
+  }
+  cublasSetStream(g_cublas, static_cast<cudaStream_t>(stream));
+  const float alpha = 1.0f, beta = 0.0f;
+  cublasStatus_t s;
+  if (c_col_major) {
+    s = cublasGemmEx(g_cublas, CUBLAS_OP_T, CUBLAS_OP_N, M, N, K, &alpha, A, CUDA_R_16BF, K, B,
+                     CUDA_R_16BF, K, &beta, C, CUDA_R_16BF, M, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+  } else {
+    s = cublasGemmEx(g_cublas, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, B, CUDA_R_16BF, K, A,
+                     CUDA_R_16BF, K, &beta, C, CUDA_R_16BF, N, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+  }
+  g_last_status = static_cast<int>(s);
+  return s == CUBLAS_STATUS_SUCCESS ? 0 : 1;
+}
+
+// Row-major C[M,N] through cublasLtMatmul with the heuristic's first algorithm.
+int b200_baseline_cublaslt_gemm_bf16(int M, int N, int K, const void* A, const void* B, void* C,
+                                     void* stream) {
+  if (g_lt == nullptr) {
+    cublasStatus_t s = cublasLtCreate(&g_lt);
+    if (s != CUBLAS_STATUS_SUCCESS) {
+      g_last_status = static_cast<int>(s);
+      return 1;
+    }
+    if (cudaMalloc(&g_lt_workspace, kLtWorkspaceBytes) != cudaSuccess) return 1;
+  }
+  cublasLtMatmulDesc_t op = nullptr;
+  cublasLtMatrixLayout_t la = nullptr, lb = nullptr, lc = nullptr;
+  cublasLtMatmulPreference_t pref = nullptr;
+  cublasStatus_t s = cublasLtMatmulDescCreate(&op, CUBLAS_COMPUTE_32F, CUDA_R_32F);
+  const cublasOperation_t opT = CUBLAS_OP_T, opN = CUBLAS_OP_N;
+  if (s == CUBLAS_STATUS_SUCCESS) s = cublasLtMatmulDescSetAttribute(op, CUBLASLT_MATMUL_DESC_TRANSA, &opT, sizeof(opT));
+  if (s == CUBLAS_STATUS_SUCCESS) s = cublasLtMatmulDescSetAttribute(op, CUBLASLT_MATMUL_DESC_TRANSB, &opN, sizeof(opN));
+  // column-major view: C^T (N x M, ld N) = B^T-view(K x N, ld K)^T * A-view(K x M, ld K)
+  if (s == CUBLAS_STATUS_SUCCESS) s = cublasLtMatrixLayoutCreate(&la, CUDA_R_16BF, K, N, K);
+  if (s == CUBLAS_STATUS_SUCCESS) s = cublasLtMatrixLayoutCreate(&lb, CUDA_R_16BF, K, M, K);
+  if (s == CUBLAS_STATUS_SUCCESS) s = cublasLtMatrixLayoutCreate(&lc, CUDA_R_16BF, N, M, N);
+  if (s == CUBLAS_STATUS_SUCCESS) s = cublasLtMatmulPreferenceCreate(&pref);
+  size_t ws = kLtWorkspaceBytes;
+  if (s == CUBLAS_STATUS_SUCCESS)
+    s = cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &ws, sizeof(ws));
+  cublasLtMatmulHeuristicResult_t heur;
+  int found = 0;
+  if (s == CUBLAS_STATUS_SUCCESS) s = cublasLtMatmulAlgoGetHeuristic(g_lt, op, la, lb, lc, lc, pref, 1, &heur, &found);
+  if (s == CUBLAS_STATUS_SUCCESS && found == 0) s = CUBLAS_STATUS_NOT_SUPPORTED;
+  const float alpha = 1.0f, beta = 0.0f;
+  if (s == CUBLAS_STATUS_SUCCESS)
+    s = cublasLtMatmul(g_lt, op, &alpha, B, la, A, lb, &beta, C, lc, C, lc, &heur.algo, g_lt_workspace,
+                       kLtWorkspaceBytes, static_cast<cudaStream_t>(stream));
+  if (pref) cublasLtMatmulPreferenceDestroy(pref);
+  if (lc) cublasLtMatrixLayoutDestroy(lc);
+  if (lb) cublasLtMatrixLayoutDestroy(lb);
+  if (la) cublasLtMatrixLayoutDestroy(la);
+  if (op) cublasLtMatmulDescDestroy(op);
+  g_last_status = static_cast<int>(s);
+  return s == CUBLAS_STATUS_SUCCESS ? 0 : 1;
+}
+
+}  // extern "C"

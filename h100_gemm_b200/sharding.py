@@ -1,0 +1,101 @@
+"""M-sharded multi-GPU GEMM: host-side logic (one process per GPU, torch.distributed plumbing).
+
+Rows of A and C are split into contiguous shards, one per rank; B is replicated. Shards are
+independent, so computing C needs NO collective; an all-gather of C over NCCL/NVLink is optional
+and, when asked for, is issued per row chunk on a side stream so that it overlaps the GEMM of
+the next chunk. The reference has no multi-GPU path (it is a single-GPU benchmark); this module
+covers the M-sharded configuration of the build's benchmark matrix.
+
+The compute step is injected (`gemm_fn`), so the partitioning, chunking and gather logic run
+unchanged under the gloo backend on CPU in the tests.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Tuple
+
+
+def shard_rows(M: int, world: int, rank: int, align: int = 1) -> Tuple[int, int]:
+    """Half-open row range of `rank`: equal shards of ceil(M/world) rounded up to `align` rows;
+    trailing ranks may get fewer (or zero) rows."""
+    if world < 1 or not (0 <= rank < world) or M < 0 or align < 1:
+        raise ValueError("bad shard arguments")
+    per = (M + world - 1) // world
+    per = (per + align - 1) // align * align
+    begin = min(M, rank * per)
+    return begin, min(M, begin + per)
+
+
+def chunk_rows(rows: int, chunks: int, align: int = 256) -> List[Tuple[int, int]]:
+    """Splits a shard of `rows` rows into at most `chunks` contiguous pieces of `align`-row
+    multiples (the last piece takes the remainder)."""
+    if rows <= 0:
+        return []
+    chunks = max(1, chunks)
+    per = (rows + chunks - 1) // chunks
+    per = max(align, (per + align - 1) // align * align)
+    return [(r, min(rows, r + per)) for r in range(0, rows, per)]
+
+
+def max_over_ranks(value: float, device=None) -> float:
+    """Timing rule for every multi-rank number: the slowest rank defines the step."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return float(value)
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+class ShardedGemm:
+    """C[M,N] = A[M,K] @ B[N,K]^T with A and C row-sharded over the ranks of a process group.
+
+    a_shard : this rank's rows of A, [rows, K]
+    b       : the full B, [N, K] (replicated)
+    gemm_fn : callable(a_rows, b, out_rows) computing out_rows = a_rows @ b^T in place
+    """
+
+    def __init__(self, M: int, a_shard, b, gemm_fn: Callable, group=None):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.M = M
+        self.a, self.b, self.gemm_fn = a_shard, b, gemm_fn
+        self.begin, self.end = shard_rows(M, self.world, self.rank)
+        if a_shard.shape[0] != self.end - self.begin:
+            raise ValueError("a_shard does not match this rank's row range")
+        if M % self.world != 0:
+            raise ValueError("M must divide evenly over the ranks for the gathered layout")
+        self.rows = M // self.world
+
+    def compute(self, out_shard) -> None:
+        """No collective: every rank fills its own rows."""
+        self.gemm_fn(self.a, self.b, out_shard)
+
+    def compute_and_gather(self, out_full, chunks: int = 4, comm_stream=None) -> None:
+        """Fills the FULL C on every rank. Chunk j of every rank's shard is gathered while chunk
+        j+1 is being multiplied (side stream on CUDA; sequential under gloo)."""
+        import torch
+        rows, N = self.rows, out_full.shape[1]
+        pieces = chunk_rows(rows, chunks)
+        use_cuda = out_full.is_cuda
+        main = torch.cuda.current_stream() if use_cuda else None
+        handles = []
+        for (r0, r1) in pieces:
+            mine = out_full[self.begin + r0:self.begin + r1]
+            self.gemm_fn(self.a[r0:r1], self.b, mine)
+            outs = [out_full[p * rows + r0:p * rows + r1] for p in range(self.world)]
+            if self.world == 1:
+                continue
+            if use_cuda and comm_stream is not None:
+                comm_stream.wait_stream(main)
+                with torch.cuda.stream(comm_stream):
+                    handles.append(self.dist.all_gather(outs, mine, group=self.group, async_op=True))
+            else:
+                self.dist.all_gather(outs, mine, group=self.group)
+        for h in handles:
+            h.wait()
+        if use_cuda and comm_stream is not None:
+            main.wait_stream(comm_stream)
