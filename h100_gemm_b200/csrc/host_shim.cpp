@@ -37,7 +37,7 @@ void hs_tile_coord(int tiles_m, int tiles_n, int batch, int group, int raster, i
   out[2] = c.b;
 }
 
-// Writes up to cap segments (tile, k_begin, k_end, slot) of one worker; returns the count.
+// Writes up to cap segments (tile, k_begin, k_end, slot, finish) of one worker; returns the count.
 int hs_segments(int tiles_m, int tiles_n, int batch, int k_tiles, int mode, int split_k, int workers,
                 int worker, int* out, int cap) {
   SchedParams p = make(tiles_m, tiles_n, batch, k_tiles, 8, 0, mode, split_k, workers);
@@ -46,10 +46,11 @@ int hs_segments(int tiles_m, int tiles_n, int batch, int k_tiles, int mode, int 
   int n = 0;
   while (it.next(s)) {
     if (n < cap) {
-      out[4 * n + 0] = s.tile;
-      out[4 * n + 1] = s.k_begin;
-      out[4 * n + 2] = s.k_end;
-      out[4 * n + 3] = s.slot;
+      out[5 * n + 0] = s.tile;
+      out[5 * n + 1] = s.k_begin;
+      out[5 * n + 2] = s.k_end;
+      out[5 * n + 3] = s.slot;
+      out[5 * n + 4] = s.finish;
     }
     ++n;
   }
@@ -60,6 +61,12 @@ int hs_tile_slots(int tiles_m, int tiles_n, int batch, int k_tiles, int mode, in
                   int tile, int* out, int cap) {
   SchedParams p = make(tiles_m, tiles_n, batch, k_tiles, 8, 0, mode, split_k, workers);
   return tile_partial_slots(p, tile, out, cap);
+}
+
+int hs_streamk_contributors(int tiles_m, int tiles_n, int batch, int k_tiles, int workers, int worker,
+                            int tile, int* first) {
+  SchedParams p = make(tiles_m, tiles_n, batch, k_tiles, 8, 0, kStreamK, 1, workers);
+  return streamk_contributors(p, worker, tile, first);
 }
 
 long long hs_num_slots(int tiles_m, int tiles_n, int batch, int k_tiles, int mode, int split_k, int workers) {

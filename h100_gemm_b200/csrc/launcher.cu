@@ -12,9 +12,11 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdint>
 #include <cstring>
 #include <map>
+#include <random>
 #include <mutex>
 #include <tuple>
 #include <vector>
@@ -323,7 +325,7 @@ b200_gemm_cfg default_cfg(int batch, int M, int N, int K) {
     // Few rows: one CTA per tile, narrower tiles, and an even split of the K loop over all SMs
     // so that every SM streams the same share of B.
     c.cluster_m = 1;
-    c.block_n = 128;
+    c.block_n = M <= 64 ? 64 : 128;  // narrower tiles leave room for a deeper B ring
     c.sched = kStreamK;
   }
   return c;
@@ -340,11 +342,10 @@ int resolve_plan(const b200_gemm_cfg& c, Plan* p) {
   p->kernel = find_kernel(bn, p->pair);
   if (p->kernel == nullptr) return B200_ERR_UNSUPPORTED_CFG;
   if (c.stages < 0) return B200_ERR_INVALID_ARG;
-  p->stages = c.stages == 0 ? p->kernel->max_stages : c.stages;
+  p->stages = c.stages;  // 0 = as many as fit; settled by fit_stages() once the A tile is known
   if (p->stages > kMaxStages) return B200_ERR_UNSUPPORTED_CFG;
-  if (p->stages < 2) return B200_ERR_UNSUPPORTED_CFG;
-  if (p->stages > p->kernel->max_stages) return B200_ERR_SMEM;
-  p->smem = smem_bytes_for(*p->kernel, p->stages);
+  if (p->stages == 1) return B200_ERR_UNSUPPORTED_CFG;
+  p->smem = 0;
   if (c.sched < 0 || c.sched > 2) return B200_ERR_INVALID_ARG;
   p->mode = c.sched;
   p->split_k = c.split_k <= 1 ? 1 : c.split_k;
@@ -360,6 +361,24 @@ int resolve_plan(const b200_gemm_cfg& c, Plan* p) {
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// Rows of A staged per CTA and K-tile: a full 128-row tile, or M rounded up to 8 when a single
+// CTA tile already covers all of M (the MMA's remaining rows feed outputs that are never stored).
+int a_rows_for(const Plan& p, int M) {
+  if (p.pair || M >= kCtaRows) return kCtaRows;
+  return (M + 7) / 8 * 8;
+}
+
+// Settles the ring depth and the dynamic shared-memory size for a given A tile height.
+int fit_stages(Plan* p, int a_rows) {
+  const int stage_bytes = a_rows * kBlockK * 2 + (p->kernel->stage_bytes - kCtaRows * kBlockK * 2);
+  int max_stages = (232448 - 1024 - kEpiBytes - kBarrierBytes) / stage_bytes;
+  if (max_stages > kMaxStages) max_stages = kMaxStages;
+  if (p->stages == 0) p->stages = max_stages;
+  if (p->stages > max_stages) return B200_ERR_SMEM;
+  p->smem = 1024 + p->stages * stage_bytes + kEpiBytes + kBarrierBytes;
+  return B200_OK;
+}
+
 struct Problem {
   int batch, M, N, K;          // as the kernel sees them (after a column-major swap)
   const void* A;
@@ -368,14 +387,15 @@ struct Problem {
   long long strideA, strideB, strideC;
 };
 
-// Workspace layout: [fp32 partial slots][re-pitched A][re-pitched B]
+// Workspace layout: [stream-K flags][fp32 partial slots][re-pitched A][re-pitched B]
 struct WorkspaceLayout {
+  size_t flag_bytes;
   size_t partial_bytes;
   size_t a_bytes;
   size_t b_bytes;
   int k_pitch;
   bool repitch;
-  size_t total() const { return partial_bytes + a_bytes + b_bytes; }
+  size_t total() const { return flag_bytes + partial_bytes + a_bytes + b_bytes; }
 };
 
 bool needs_repitch(const Problem& pr) {
@@ -411,6 +431,7 @@ void build_sched(const Plan& p, const Problem& pr, int workers, SchedParams* s) 
 WorkspaceLayout workspace_layout(const Plan& p, const Problem& pr, const SchedParams& s) {
   WorkspaceLayout w{};
   const int block_m = kCtaRows * (p.pair ? 2 : 1);
+  w.flag_bytes = s.mode == kStreamK ? align_up(static_cast<size_t>(sched_num_slots(s)) * 8 * sizeof(unsigned long long), 256) : 0;
   w.partial_bytes =
       align_up(static_cast<size_t>(sched_num_slots(s)) * block_m * p.kernel->bn * sizeof(float), 256);
   w.repitch = needs_repitch(pr);
@@ -420,6 +441,18 @@ WorkspaceLayout workspace_layout(const Plan& p, const Problem& pr, const SchedPa
     w.b_bytes = align_up(static_cast<size_t>(pr.batch) * pr.N * w.k_pitch * 2, 256);
   }
   return w;
+}
+
+// Stream-K marks a partial tile as written by storing the launch's epoch in its flag words. The
+// epochs of one process start at a random 64-bit value and count up, so stale workspace contents
+// (any earlier launch, or uninitialised memory) do not pass for this launch's.
+unsigned long long next_epoch() {
+  static std::atomic<unsigned long long> counter{[] {
+    std::random_device rd;
+    unsigned long long v = (static_cast<unsigned long long>(rd()) << 32) ^ rd();
+    return v | (1ull << 63);
+  }()};
+  return counter.fetch_add(1) + 1;
 }
 
 int nominal_workers(const Plan& p, int sm_count) {
@@ -462,6 +495,10 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
     pr.strideB = strideA;
   }
 
+  const int a_rows = a_rows_for(plan, pr.M);
+  rc = fit_stages(&plan, a_rows);
+  if (rc != B200_OK) return rc;
+
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState* st = nullptr;
   rc = get_device_state(&st);
@@ -485,7 +522,7 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   long long a_pitch = pr.K, b_pitch = pr.K;
   long long a_bstride = pr.strideA, b_bstride = pr.strideB;
   if (ws.repitch) {
-    uint8_t* base = static_cast<uint8_t*>(workspace) + ws.partial_bytes;
+    uint8_t* base = static_cast<uint8_t*>(workspace) + ws.flag_bytes + ws.partial_bytes;
     uint16_t* a_dst = reinterpret_cast<uint16_t*>(base);
     uint16_t* b_dst = reinterpret_cast<uint16_t*>(base + ws.a_bytes);
     const int threads = 256;
@@ -513,7 +550,7 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
                      (pr.batch == 1 || pr.strideC % 8 == 0);
 
   CUtensorMap map_a, map_b, map_c;
-  rc = make_tensor_map(&map_a, a_src, pr.K, pr.M, pr.batch, a_pitch * 2, a_bstride * 2, kBlockK, kCtaRows);
+  rc = make_tensor_map(&map_a, a_src, pr.K, pr.M, pr.batch, a_pitch * 2, a_bstride * 2, kBlockK, a_rows);
   if (rc != B200_OK) return rc;
   rc = make_tensor_map(&map_b, b_src, pr.K, pr.N, pr.batch, b_pitch * 2, b_bstride * 2, kBlockK,
                        plan.kernel->b_rows_cta);
@@ -535,7 +572,13 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   args.C = static_cast<__nv_bfloat16*>(pr.C);
   args.ldc = pr.N;
   args.c_batch_stride = pr.strideC;
-  args.partial = ws.partial_bytes ? static_cast<float*>(workspace) : nullptr;
+  args.flags = ws.flag_bytes ? static_cast<unsigned long long*>(workspace) : nullptr;
+  args.partial = ws.partial_bytes
+                     ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ws.flag_bytes)
+                     : nullptr;
+  args.epoch = next_epoch();
+  args.a_rows = a_rows;
+  args.a_stage_bytes = a_rows * kBlockK * 2;
   args.alpha = alpha;
   args.beta = beta;
   args.scale = (alpha != 1.0f || beta != 0.0f) ? 1 : 0;
@@ -556,7 +599,7 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   lc.numAttrs = 1;
   B200_CUDA_TRY(cudaLaunchKernelEx(&lc, plan.kernel->fn, map_a, map_b, map_c, args));
 
-  if (sched_num_slots(args.sched) > 0) {
+  if (args.sched.mode == kSplitK && sched_num_slots(args.sched) > 0) {
     const int block_m = kCtaRows * (plan.pair ? 2 : 1);
     const int blocks = args.sched.num_tiles < st->sm_count * 4 ? args.sched.num_tiles : st->sm_count * 4;
     fixup_kernel<<<blocks, 256, 0, stream>>>(args, block_m, plan.kernel->bn);
@@ -644,6 +687,8 @@ int b200_gemm_default_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg) {
   *cfg = default_cfg(batch, M, N, K);
   Plan plan;
   int rc = resolve_plan(*cfg, &plan);
+  if (rc != B200_OK) return rc;
+  rc = fit_stages(&plan, a_rows_for(plan, M));
   if (rc != B200_OK) return rc;
   cfg->stages = plan.stages;
   return B200_OK;

@@ -51,6 +51,7 @@ enum DeviceStatus : unsigned int {
   kStatusMmaFullTimeout = 2,    // MMA issuer waited for full[s]
   kStatusMmaTmemTimeout = 3,    // MMA issuer waited for tmem_empty[a]
   kStatusEpilogueTimeout = 4,   // epilogue waited for tmem_full[a]
+  kStatusStreamKTimeout = 5,    // stream-K finisher waited for another worker's partial tile
   kStatusSelfTestTimeout = 9,   // the bounded-wait self-test (an mbarrier nothing arrives on)
 };
 
@@ -63,6 +64,10 @@ struct GemmArgs {
   long long ldc;              // elements between rows of C
   long long c_batch_stride;   // elements between batches of C
   float* partial;             // fp32 slots for split-K / stream-K partial tiles
+  unsigned long long* flags;  // stream-K: 8 words per slot (CTA rank x TMEM quadrant), set to `epoch`
+  unsigned long long epoch;   // value that marks a slot as written by THIS launch
+  int a_rows;                 // rows of A staged per CTA and K-tile (128, or fewer when M < 128)
+  int a_stage_bytes;          // a_rows * 128
   float alpha, beta;
   int scale;                  // 1: C = acc * alpha + beta (the scalar-beta rule of reference.h:40)
   unsigned int* status;       // 4 words: code, block, tile, detail
@@ -76,7 +81,7 @@ struct KernelTraits {
   static constexpr int kBRowsCta = BN / kCtaGroup;
   static constexpr int kABytes = kCtaRows * kBlockK * 2;
   static constexpr int kBBytes = kBRowsCta * kBlockK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;  // with a full 128-row A tile
   static constexpr int kTmemCols = (kAccStages * BN <= 32)    ? 32
                                    : (kAccStages * BN <= 64)  ? 64
                                    : (kAccStages * BN <= 128) ? 128
@@ -141,11 +146,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const int worker = PAIR ? static_cast<int>(ptx::cluster_id_x()) : static_cast<int>(blockIdx.x);
 
   const int stages = args.stages;
+  // A stage holds a_rows x 64 of A followed by the B tile. With fewer than 128 rows of A staged
+  // (M < 128) the MMA still reads 128 rows: the extra rows are whatever follows in shared
+  // memory, they only feed accumulator rows >= M, which are never written out.
+  const uint32_t stage_bytes = static_cast<uint32_t>(args.a_stage_bytes) + T::kBBytes;
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t epi_base = smem_base + static_cast<uint32_t>(stages) * T::kStageBytes;
+  const uint32_t epi_base = smem_base + static_cast<uint32_t>(stages) * stage_bytes;
   const uint32_t bar_base = epi_base + kEpiBytes;
-  auto a_addr = [&](int s) { return smem_base + static_cast<uint32_t>(s) * T::kStageBytes; };
-  auto b_addr = [&](int s) { return a_addr(s) + T::kABytes; };
+  auto a_addr = [&](int s) { return smem_base + static_cast<uint32_t>(s) * stage_bytes; };
+  auto b_addr = [&](int s) { return a_addr(s) + static_cast<uint32_t>(args.a_stage_bytes); };
   auto full_bar = [&](int s) { return bar_base + 8u * static_cast<uint32_t>(s); };
   auto empty_bar = [&](int s) { return bar_base + 8u * static_cast<uint32_t>(kMaxStages + s); };
   auto tmem_full_bar = [&](int a) { return bar_base + 8u * static_cast<uint32_t>(2 * kMaxStages + a); };
@@ -207,7 +216,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             ok = false;
             break;
           }
-          if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), T::kStageBytes * G);
+          if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), stage_bytes * G);
           if (PAIR) {
             const uint32_t bar = full_base_leader + 8u * static_cast<uint32_t>(stage);
             ptx::tma_load_3d_pair(a_addr(stage), &map_a, bar, kt * kBlockK, row_a, tc.b);
@@ -302,7 +311,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const uint32_t tmem_acc =
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
       const bool to_slot = seg.slot >= 0;
-      const bool rows_live = to_slot || (m_slab < args.M);
+      const int row_in_tile = tile_row + static_cast<int>(lane);
+      const bool row_live = (tc.m * T::kBlockM + row_in_tile) < args.M;
+      const bool rows_live = m_slab < args.M;  // warp-uniform: any live row in this slab
+
+      // Stream-K finisher: the other workers' partial tiles to add, in K order.
+      int contrib_first = 0, contrib_count = 0;
+      bool contrib_ok = true;
+      if (seg.finish) {
+        contrib_count = streamk_contributors(args.sched, worker, seg.tile, &contrib_first);
+        if (rows_live) {
+          for (int j = 0; j < contrib_count && contrib_ok; ++j) {
+            const unsigned long long* flag =
+                args.flags + (static_cast<long long>(contrib_first + j) * 2 + cta_rank) * 4 + q;
+            const long long t0 = clock64();
+            while (ptx::ld_acquire_u64(flag) != args.epoch) {
+              if (clock64() - t0 > ptx::kWaitBudgetCycles) {
+                contrib_ok = false;
+                break;
+              }
+              __nanosleep(64);
+            }
+          }
+          contrib_ok = __all_sync(0xffffffffu, contrib_ok);
+          if (!contrib_ok && lane == 0) {
+            report_timeout(args, kStatusStreamKTimeout, seg.tile, contrib_first, abort_flag);
+          }
+        }
+      }
 
 #pragma unroll 1
       for (int c = 0; c < BN / kEpiChunkCols; ++c) {
@@ -325,20 +361,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (!live) continue;
 
         if (to_slot) {
-          // fp32 partial tile: slot[row][col], row-major, tile-local coordinates.
-          float* dst = args.partial +
-                       (static_cast<long long>(seg.slot) * T::kBlockM + tile_row + lane) * BN +
-                       c * kEpiChunkCols;
+          // fp32 partial tile: slot[row][col], row-major, tile-local coordinates; rows >= M are
+          // never read back and are not written.
+          if (row_live) {
+            float* dst = args.partial +
+                         (static_cast<long long>(seg.slot) * T::kBlockM + row_in_tile) * BN +
+                         c * kEpiChunkCols;
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < 2; ++h) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 f = make_float4(__uint_as_float(v[h][j]), __uint_as_float(v[h][j + 1]),
-                                     __uint_as_float(v[h][j + 2]), __uint_as_float(v[h][j + 3]));
-              *reinterpret_cast<float4*>(dst + h * 32 + j) = f;
+              for (int j = 0; j < 32; j += 4) {
+                float4 f = make_float4(__uint_as_float(v[h][j]), __uint_as_float(v[h][j + 1]),
+                                       __uint_as_float(v[h][j + 2]), __uint_as_float(v[h][j + 3]));
+                __stcg(reinterpret_cast<float4*>(dst + h * 32 + j), f);
+              }
             }
           }
           continue;
+        }
+
+        if (seg.finish && row_live) {
+          for (int j = 0; j < contrib_count; ++j) {
+            const float* src = args.partial +
+                               (static_cast<long long>(contrib_first + j) * T::kBlockM + row_in_tile) * BN +
+                               c * kEpiChunkCols;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                const float4 f = __ldcg(reinterpret_cast<const float4*>(src + h * 32 + i));
+                v[h][i + 0] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][i + 0]), f.x));
+                v[h][i + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][i + 1]), f.y));
+                v[h][i + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][i + 2]), f.z));
+                v[h][i + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][i + 3]), f.w));
+              }
+            }
+          }
         }
 
         if (args.scale) {
@@ -391,6 +449,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           ptx::tma_store_commit();
         }
         ++store_count;
+      }
+      if (to_slot && args.sched.mode == kStreamK) {
+        // Publish this warp's rows of the partial tile: every lane's stores, then the flag.
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::st_release_u64(args.flags + (static_cast<long long>(seg.slot) * 2 + cta_rank) * 4 + q,
+                              args.epoch);
+        }
       }
       if (++acc == kAccStages) {
         acc = 0;

@@ -7,8 +7,12 @@
 //   mode 1  split-K       : every tile is cut into `split_k` K-slices; partial sums go to slots
 //   mode 2  stream-K      : the tiles x k_tiles iteration space is cut into W equal contiguous
 //                           ranges; a range's first/last tile may be partial
-// Partial segments carry a slot index into an fp32 workspace; a fix-up pass sums the slots of a
-// tile in a fixed order, so results do not depend on timing.
+// Partial segments carry a slot index into an fp32 workspace. Split-K slots are summed in slot
+// order by a fix-up pass. Under stream-K a tile cut across workers is finished inside the GEMM
+// kernel: the worker holding the tile's head (k_begin == 0) adds the partial tiles of the workers
+// holding its later K-ranges, in K order. Those partials are always the FIRST segment of their
+// worker, so the finisher never waits on work that is queued behind its own. Either way the
+// summation order is fixed and results do not depend on timing.
 //
 // Everything here compiles for the host as well, so coverage (every (tile, k) iteration visited
 // exactly once) is tested exhaustively without a GPU.
@@ -49,7 +53,9 @@ struct Segment {
   int tile;     // linear tile id
   int k_begin;  // first K-tile (inclusive)
   int k_end;    // last K-tile (exclusive)
-  int slot;     // < 0: this segment produces the final output; >= 0: fp32 partial slot index
+  int slot;     // >= 0: write the fp32 partial tile to this slot; < 0: write the output
+  int finish;   // 1: (stream-K) before writing the output, add the partial slots of the workers
+                //    that hold the rest of this tile's K range (see streamk_contributors)
 };
 
 // Linear tile id -> coordinates. Inside a batch, tiles are grouped into bands of `group` tiles
@@ -91,7 +97,7 @@ B200_SCHED_HD int splitk_begin(const SchedParams& p, int s) {
 // Number of fp32 partial slots the workspace must hold.
 B200_SCHED_HD long long sched_num_slots(const SchedParams& p) {
   if (p.mode == kSplitK) return p.split_k > 1 ? static_cast<long long>(p.split_k) * p.num_tiles : 0;
-  if (p.mode == kStreamK) return 2ll * p.num_workers;
+  if (p.mode == kStreamK) return p.num_workers;  // one per worker: its first segment
   return 0;
 }
 
@@ -123,6 +129,7 @@ struct WorkIter {
       s.k_begin = 0;
       s.k_end = p.k_tiles;
       s.slot = -1;
+      s.finish = 0;
       cur += p.num_workers;
     } else if (p.mode == kSplitK) {
       const int slice = static_cast<int>(cur / p.num_tiles);
@@ -130,6 +137,7 @@ struct WorkIter {
       s.k_begin = splitk_begin(p, slice);
       s.k_end = splitk_begin(p, slice + 1);
       s.slot = p.split_k > 1 ? slice * p.num_tiles + s.tile : -1;
+      s.finish = 0;
       cur += p.num_workers;
     } else {
       s.tile = static_cast<int>(cur / p.k_tiles);
@@ -138,8 +146,10 @@ struct WorkIter {
       long long stop = tile_first + p.k_tiles;
       if (stop > end) stop = end;
       s.k_end = static_cast<int>(stop - tile_first);
-      const bool full = (s.k_begin == 0) && (s.k_end == p.k_tiles);
-      s.slot = full ? -1 : 2 * worker + (cur == range_begin ? 0 : 1);
+      // A range that starts inside a tile contributes a partial; the range holding the tile's
+      // head finishes it when the tile's tail belongs to other workers.
+      s.slot = s.k_begin > 0 ? worker : -1;
+      s.finish = (s.k_begin == 0 && s.k_end < p.k_tiles) ? 1 : 0;
       cur = stop;
     }
     return true;
@@ -159,25 +169,17 @@ B200_SCHED_HD int tile_partial_slots(const SchedParams& p, int tile, int* slots,
     }
     return n;
   }
-  if (p.mode != kStreamK) return 0;
-  const long long first = static_cast<long long>(tile) * p.k_tiles;
-  const long long last = first + p.k_tiles;
-  const long long total = sched_total_iters(p);
-  // Worker that owns iteration `first`: largest w with streamk_begin(w) <= first.
-  int w = static_cast<int>((first * p.num_workers) / total);
-  while (w + 1 < p.num_workers && streamk_begin(p, w + 1) <= first) ++w;
-  while (w > 0 && streamk_begin(p, w) > first) --w;
-  for (; w < p.num_workers; ++w) {
-    const long long rb = streamk_begin(p, w);
-    const long long re = streamk_begin(p, w + 1);
-    if (rb >= last) break;
-    if (re <= first || re == rb) continue;
-    const long long sb = rb > first ? rb : first;
-    const long long se = re < last ? re : last;
-    if (sb == first && se == last) return 0;  // one worker produced the whole tile
-    if (n < cap) slots[n] = 2 * w + (sb == rb ? 0 : 1);
-    ++n;
-  }
+  return 0;
+}
+
+// Stream-K: the workers whose partial slots complete the tile that `worker` holds the head of.
+// They are the consecutive workers after `worker` whose ranges start before the tile ends;
+// worker w's partial lives in slot w. Returns their count; *first = worker + 1.
+B200_SCHED_HD int streamk_contributors(const SchedParams& p, int worker, int tile, int* first) {
+  const long long tile_end = (static_cast<long long>(tile) + 1) * p.k_tiles;
+  *first = worker + 1;
+  int n = 0;
+  for (int w = worker + 1; w < p.num_workers && streamk_begin(p, w) < tile_end; ++w) ++n;
   return n;
 }
 

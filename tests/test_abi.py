@@ -60,9 +60,9 @@ def test_workspace_sizes(lib):
     # split-K: split_k * tiles fp32 tiles
     cfg = C(block_n=128, cluster_m=1, sched=1, split_k=4)
     assert api.workspace_bytes(1, 128, 1024, 4096, cfg) == 4 * 8 * 128 * 128 * 4
-    # stream-K: two slots per worker (148 SMs assumed without a device)
+    # stream-K: one slot per worker plus 8 flag words each (148 SMs assumed without a device)
     cfg = C(block_n=128, cluster_m=1, sched=2)
-    assert api.workspace_bytes(1, 64, 28672, 8192, cfg) == 2 * 148 * 128 * 128 * 4
+    assert api.workspace_bytes(1, 64, 28672, 8192, cfg) == 148 * 128 * 128 * 4 + 148 * 64
     # invalid sizes / unsupported configurations need nothing and report nothing
     assert api.workspace_bytes(1, 0, 10, 10, None) == 0
     assert api.workspace_bytes(1, 128, 128, 128, C(block_n=100)) == 0

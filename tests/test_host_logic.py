@@ -16,10 +16,10 @@ def shim():
 
 
 def segments(shim, tm, tn, batch, kt, mode, split, workers, w):
-    buf = (ctypes.c_int * (4 * 8192))()
+    buf = (ctypes.c_int * (5 * 8192))()
     n = shim.hs_segments(tm, tn, batch, kt, mode, split, workers, w, buf, 8192)
     assert n <= 8192
-    return [tuple(buf[4 * i:4 * i + 4]) for i in range(n)]
+    return [tuple(buf[5 * i:5 * i + 5]) for i in range(n)]
 
 
 def test_instruction_descriptor_bits(shim):
@@ -84,14 +84,23 @@ def test_every_k_iteration_is_visited_exactly_once(shim, tm, tn, batch, kt, mode
     visits = defaultdict(int)
     slots_by_tile = defaultdict(list)
     used_slots = set()
+    per_worker = {}
     for w in range(workers):
-        for tile, kb, ke, slot in segments(shim, tm, tn, batch, kt, mode, split, workers, w):
+        segs = segments(shim, tm, tn, batch, kt, mode, split, workers, w)
+        per_worker[w] = segs
+        for i, (tile, kb, ke, slot, finish) in enumerate(segs):
             assert 0 <= tile < tiles and 0 <= kb < ke <= kt
             for k in range(kb, ke):
                 visits[(tile, k)] += 1
             full = kb == 0 and ke == kt
-            if mode != 1:
-                assert (slot < 0) == full
+            if mode == 0:
+                assert slot < 0 and finish == 0
+            if mode == 2:
+                # partials are contributed only by a worker's first segment, into its own slot;
+                # the holder of the tile's head finishes it
+                assert (slot >= 0) == (kb > 0) and (slot < 0 or (slot == w and i == 0))
+                assert finish == (1 if (kb == 0 and ke < kt) else 0)
+                assert not full or (slot < 0 and finish == 0)
             if slot >= 0:
                 assert slot not in used_slots, "two segments share a partial slot"
                 used_slots.add(slot)
@@ -99,18 +108,36 @@ def test_every_k_iteration_is_visited_exactly_once(shim, tm, tn, batch, kt, mode
     assert len(visits) == tiles * kt and set(visits.values()) == {1}
     nslots = shim.hs_num_slots(tm, tn, batch, kt, mode, split, workers)
     assert all(s < nslots for s in used_slots)
-    # The fix-up pass must find exactly the slots that were written, in K order.
     buf = (ctypes.c_int * 64)()
-    for tile in range(tiles):
-        n = shim.hs_tile_slots(tm, tn, batch, kt, mode, split, workers, tile, buf, 64)
-        assert n <= 64
-        want = [s for _, s in sorted(slots_by_tile[tile])]
-        assert [buf[i] for i in range(n)] == want
+    if mode == 1:
+        # the fix-up pass must find exactly the slots that were written, in K order
+        for tile in range(tiles):
+            n = shim.hs_tile_slots(tm, tn, batch, kt, mode, split, workers, tile, buf, 64)
+            assert n <= 64
+            assert [buf[i] for i in range(n)] == [s for _, s in sorted(slots_by_tile[tile])]
+    if mode == 2:
+        # every finisher's contributors are the next workers' first segments and tile the rest of K
+        first = ctypes.c_int()
+        for w, segs in per_worker.items():
+            for tile, kb, ke, slot, finish in segs:
+                if not finish:
+                    continue
+                n = shim.hs_streamk_contributors(tm, tn, batch, kt, workers, w, tile, ctypes.byref(first))
+                assert n >= 1 and first.value == w + 1
+                pos = ke
+                for c in range(first.value, first.value + n):
+                    ctile, ckb, cke, cslot, cfin = per_worker[c][0]
+                    assert ctile == tile and ckb == pos and cslot == c and cfin == 0
+                    pos = cke
+                assert pos == kt
+        # and every contributed slot is consumed by exactly one finisher
+        finished_tiles = {tile for segs in per_worker.values() for tile, _, _, _, f in segs if f}
+        assert set(slots_by_tile) == finished_tiles
 
 
 def test_streamk_balances_work(shim):
     # Skinny decode shape: 1 x 224 tiles of 128 K-tiles over 148 workers.
     loads = []
     for w in range(148):
-        loads.append(sum(ke - kb for _, kb, ke, _ in segments(shim, 1, 224, 1, 128, 2, 1, 148, w)))
+        loads.append(sum(ke - kb for _, kb, ke, _, _ in segments(shim, 1, 224, 1, 128, 2, 1, 148, w)))
     assert sum(loads) == 224 * 128 and max(loads) - min(loads) <= 1
