@@ -13,7 +13,11 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Optional
 
-_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libb200gemm.so"
+import os
+
+# B200_GEMM_LIBRARY points the binding at another build of the same C ABI (A/B comparisons).
+_LIB_PATH = Path(os.environ.get("B200_GEMM_LIBRARY") or
+                 Path(__file__).resolve().parent / "lib" / "libb200gemm.so")
 _lib = None
 
 STATUS_OK = 0
@@ -34,7 +38,7 @@ class GemmError(RuntimeError):
 class _Cfg(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in (
         "block_m", "block_n", "block_k", "stages", "cluster_m", "cluster_n", "sched", "split_k",
-        "raster", "group", "c_col_major", "max_ctas")]
+        "raster", "group", "c_col_major", "max_ctas", "epilogue")]
 
 
 @dataclass
@@ -52,11 +56,12 @@ class GemmConfig:
     group: int = 0
     c_col_major: int = 0
     max_ctas: int = 0
+    epilogue: int = 0
 
     def _c(self) -> _Cfg:
         return _Cfg(self.block_m, self.block_n, self.block_k, self.stages, self.cluster_m,
                     self.cluster_n, self.sched, self.split_k, self.raster, self.group,
-                    self.c_col_major, self.max_ctas)
+                    self.c_col_major, self.max_ctas, self.epilogue)
 
 
 def library() -> ctypes.CDLL:
@@ -87,6 +92,9 @@ def library() -> ctypes.CDLL:
     lib.b200_reference_gpu_gemm_bf16.restype = ci
     lib.b200_gemm_last_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint * 4)]
     lib.b200_gemm_last_device_status.restype = ci
+    if hasattr(lib, "b200_gemm_set_profile_buffer"):  # absent from older builds of the ABI
+        lib.b200_gemm_set_profile_buffer.argtypes = [vp, sz]
+        lib.b200_gemm_set_profile_buffer.restype = ci
     lib.b200_gemm_selftest_bounded_wait.argtypes = [ll]
     lib.b200_gemm_selftest_bounded_wait.restype = ci
     lib.b200_gemm_strerror.argtypes = [ci]
@@ -264,6 +272,19 @@ def gemm_host(a_bits, b_bits, out_bits=None, alpha: float = 1.0, beta: float = 0
     keep, p = _cfg_ptr(cfg)
     _check(library().b200_gemm_bf16_host(M, N, K, pa, pb, pc, alpha, beta, p))
     return out_bits
+
+
+PROFILE_SLOTS = ("total", "producer_wait", "mma_wait_full", "mma_wait_tmem", "epi_wait_full", "epi_drain",
+                 "epi_busy", "tiles")
+
+
+def set_profile_buffer(buffer) -> None:
+    """Registers (or, with None, removes) a CUDA int64 tensor of 8 counters per CTA that every
+    launch fills with per-role cycle counts (see include/b200_gemm.h)."""
+    if buffer is None:
+        _check(library().b200_gemm_set_profile_buffer(None, 0))
+    else:
+        _check(library().b200_gemm_set_profile_buffer(buffer.data_ptr(), buffer.numel() * buffer.element_size()))
 
 
 def selftest_bounded_wait(budget_cycles: int = 1 << 20) -> None:

@@ -14,6 +14,7 @@
 
 #include <atomic>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <random>
@@ -140,31 +141,32 @@ using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMa
 struct KernelEntry {
   int bn;
   int pair;
+  int mt;         // 128-row sub-tiles of A per CTA
   KernelFn fn;
-  int stage_bytes;
-  int max_stages;
+  KernelFn fn_traced;  // same kernel with the cycle counters compiled in
+  int b_bytes;    // bytes of B staged per CTA and K-tile
   int b_rows_cta;
+  int block_m;    // rows of C per worker tile
+  int threads;
+  int epi_bytes;  // epilogue staging shared memory
 };
 
-template <int BN, int PAIR>
+template <int BN, int PAIR, int MT>
 KernelEntry make_entry() {
-  using T = KernelTraits<BN, PAIR>;
-  return KernelEntry{BN, PAIR, &gemm_kernel<BN, PAIR>, T::kStageBytes, T::max_stages(),
-                     T::kBRowsCta};
+  using T = KernelTraits<BN, PAIR, MT>;
+  return KernelEntry{BN,         PAIR,          MT,          &gemm_kernel<BN, PAIR, MT, 0>, &gemm_kernel<BN, PAIR, MT, 1>,
+                     T::kBBytes, T::kBRowsCta, T::kBlockM, T::kThreads,                   T::kEpiBytes};
 }
 
-const KernelEntry* find_kernel(int bn, int pair) {
+const KernelEntry* find_kernel(int bn, int pair, int mt) {
   static const KernelEntry table[] = {
-      make_entry<64, 0>(),  make_entry<128, 0>(), make_entry<192, 0>(), make_entry<256, 0>(),
-      make_entry<64, 1>(),  make_entry<128, 1>(), make_entry<192, 1>(), make_entry<256, 1>(),
+      make_entry<64, 0, 1>(),  make_entry<128, 0, 1>(), make_entry<192, 0, 1>(), make_entry<256, 0, 1>(),
+      make_entry<64, 1, 1>(),  make_entry<128, 1, 1>(), make_entry<192, 1, 1>(), make_entry<256, 1, 1>(),
+      make_entry<128, 0, 2>(), make_entry<256, 0, 2>(), make_entry<128, 1, 2>(), make_entry<256, 1, 2>(),
   };
   for (const auto& e : table)
-    if (e.bn == bn && e.pair == pair) return &e;
+    if (e.bn == bn && e.pair == pair && e.mt == mt) return &e;
   return nullptr;
-}
-
-int smem_bytes_for(const KernelEntry& e, int stages) {
-  return 1024 + stages * e.stage_bytes + kEpiBytes + kBarrierBytes;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -184,6 +186,8 @@ struct DeviceState {
 };
 
 std::mutex g_mutex;
+long long* g_profile = nullptr;      // optional device buffer for per-CTA cycle counters
+size_t g_profile_bytes = 0;
 DeviceState g_devices[64];
 EncodeTiledFn g_encode = nullptr;
 
@@ -225,12 +229,13 @@ int max_resident_workers(DeviceState& st, const KernelEntry& e, int smem, int* o
   }
   // Opt in to the device maximum once, so a later launch with fewer stages cannot shrink it.
   B200_CUDA_TRY(cudaFuncSetAttribute(e.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+  B200_CUDA_TRY(cudaFuncSetAttribute(e.fn_traced, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
   if (smem > st.smem_optin) return B200_ERR_SMEM;
   int workers = st.sm_count;
   if (e.pair) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(st.sm_count & ~1), 1, 1);
-    cfg.blockDim = dim3(kNumThreads, 1, 1);
+    cfg.blockDim = dim3(static_cast<unsigned>(e.threads), 1, 1);
     cfg.dynamicSmemBytes = static_cast<size_t>(smem);
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -296,6 +301,11 @@ int make_tensor_map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t
 // ------------------------------------------------------------------------------------------
 // Configuration
 // ------------------------------------------------------------------------------------------
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  return v ? std::atoi(v) : fallback;
+}
+
 struct Plan {
   const KernelEntry* kernel;
   int pair;
@@ -307,10 +317,14 @@ struct Plan {
   int group;
   int max_ctas;
   int c_col_major;
+  int store_tma;   // 1: TMA-store epilogue; 0: vector stores from registers
 };
 
+// Default configuration from the shape. For M > 128 the candidates are ranked by a small cost
+// model: waves of tiles over the workers x tile area per SM x a penalty for the L2 -> shared
+// memory traffic each tile shape needs per FLOP (larger tiles move fewer bytes, which on a
+// power-limited part buys clock; smaller tiles fill the machine when there are few of them).
 b200_gemm_cfg default_cfg(int batch, int M, int N, int K) {
-  (void)batch;
   (void)K;
   b200_gemm_cfg c;
   std::memset(&c, 0, sizeof(c));
@@ -318,28 +332,49 @@ b200_gemm_cfg default_cfg(int batch, int M, int N, int K) {
   c.block_k = 64;
   c.cluster_n = 1;
   c.group = 8;
-  if (M > 128) {
-    c.cluster_m = 2;
-    c.block_n = N > 128 ? 256 : 128;
-  } else {
+  if (M <= 128) {
     // Few rows: one CTA per tile, narrower tiles, and an even split of the K loop over all SMs
     // so that every SM streams the same share of B.
     c.cluster_m = 1;
     c.block_n = M <= 64 ? 64 : 128;  // narrower tiles leave room for a deeper B ring
     c.sched = kStreamK;
+    return c;
+  }
+  struct Cand {
+    int block_m, block_n, cluster_m;
+    double penalty;
+  };
+  static const Cand cands[] = {
+      {256, 256, 2, 1.00}, {128, 256, 2, 1.06}, {128, 128, 2, 1.15}, {128, 128, 1, 1.28}, {128, 64, 1, 1.45},
+  };
+  const int sms = 148;
+  double best = 0.0;
+  for (const Cand& k : cands) {
+    const long long tile_m = static_cast<long long>(k.block_m) * k.cluster_m;
+    const long long tiles = ((M + tile_m - 1) / tile_m) * ((N + k.block_n - 1) / k.block_n) * batch;
+    const long long workers = sms / k.cluster_m;
+    const long long waves = (tiles + workers - 1) / workers;
+    const double cost = static_cast<double>(waves) * k.block_m * k.block_n * k.penalty;
+    if (best == 0.0 || cost < best) {
+      best = cost;
+      c.block_m = k.block_m;
+      c.block_n = k.block_n;
+      c.cluster_m = k.cluster_m;
+    }
   }
   return c;
 }
 
 int resolve_plan(const b200_gemm_cfg& c, Plan* p) {
   if (c.block_k != 0 && c.block_k != 64) return B200_ERR_UNSUPPORTED_CFG;
-  if (c.block_m != 0 && c.block_m != 128) return B200_ERR_UNSUPPORTED_CFG;
+  if (c.block_m != 0 && c.block_m != 128 && c.block_m != 256) return B200_ERR_UNSUPPORTED_CFG;
+  const int mt = c.block_m == 256 ? 2 : 1;
   if (c.cluster_n != 0 && c.cluster_n != 1) return B200_ERR_UNSUPPORTED_CFG;
   int cm = c.cluster_m == 0 ? 1 : c.cluster_m;
   if (cm < 1 || cm > 16 || (cm & (cm - 1)) != 0) return B200_ERR_UNSUPPORTED_CFG;
   const int bn = c.block_n == 0 ? 128 : c.block_n;
   p->pair = cm >= 2 ? 1 : 0;
-  p->kernel = find_kernel(bn, p->pair);
+  p->kernel = find_kernel(bn, p->pair, mt);
   if (p->kernel == nullptr) return B200_ERR_UNSUPPORTED_CFG;
   if (c.stages < 0) return B200_ERR_INVALID_ARG;
   p->stages = c.stages;  // 0 = as many as fit; settled by fit_stages() once the A tile is known
@@ -354,6 +389,8 @@ int resolve_plan(const b200_gemm_cfg& c, Plan* p) {
   p->raster = c.raster ? 1 : 0;
   p->group = c.group > 0 ? c.group : 8;
   if (cm > 2) p->group = p->group * (cm / 2);
+  if (c.epilogue < 0 || c.epilogue > 2) return B200_ERR_INVALID_ARG;
+  p->store_tma = c.epilogue == 0 ? 1 : (c.epilogue == 1 ? 1 : 0);
   p->max_ctas = c.max_ctas;
   p->c_col_major = c.c_col_major ? 1 : 0;
   return B200_OK;
@@ -364,18 +401,24 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 // Rows of A staged per CTA and K-tile: a full 128-row tile, or M rounded up to 8 when a single
 // CTA tile already covers all of M (the MMA's remaining rows feed outputs that are never stored).
 int a_rows_for(const Plan& p, int M) {
-  if (p.pair || M >= kCtaRows) return kCtaRows;
+  if (p.pair || p.kernel->mt > 1 || M >= kCtaRows) return kCtaRows * p.kernel->mt;
   return (M + 7) / 8 * 8;
 }
 
 // Settles the ring depth and the dynamic shared-memory size for a given A tile height.
-int fit_stages(Plan* p, int a_rows) {
-  const int stage_bytes = a_rows * kBlockK * 2 + (p->kernel->stage_bytes - kCtaRows * kBlockK * 2);
-  int max_stages = (232448 - 1024 - kEpiBytes - kBarrierBytes) / stage_bytes;
+int fit_stages(Plan* p, int a_rows, int epi_bytes) {
+  const int stage_bytes = a_rows * kBlockK * 2 + p->kernel->b_bytes;
+  // With a short A tile the MMA still reads a full-height tile from the stage's base address.
+  // Whatever lies beyond the stage only feeds accumulator rows that are never stored, but it must
+  // be shared memory this CTA owns: pad the allocation by the worst over-read of the last stage.
+  const int full_a_bytes = kCtaRows * p->kernel->mt * kBlockK * 2;
+  const int over_read = full_a_bytes > stage_bytes ? full_a_bytes - stage_bytes : 0;
+  epi_bytes += over_read;
+  int max_stages = (232448 - 1024 - epi_bytes - kBarrierBytes) / stage_bytes;
   if (max_stages > kMaxStages) max_stages = kMaxStages;
   if (p->stages == 0) p->stages = max_stages;
   if (p->stages > max_stages) return B200_ERR_SMEM;
-  p->smem = 1024 + p->stages * stage_bytes + kEpiBytes + kBarrierBytes;
+  p->smem = 1024 + p->stages * stage_bytes + epi_bytes + kBarrierBytes;
   return B200_OK;
 }
 
@@ -406,7 +449,7 @@ bool needs_repitch(const Problem& pr) {
 }
 
 void build_sched(const Plan& p, const Problem& pr, int workers, SchedParams* s) {
-  const int block_m = kCtaRows * (p.pair ? 2 : 1);
+  const int block_m = p.kernel->block_m;
   s->tiles_m = (pr.M + block_m - 1) / block_m;
   s->tiles_n = (pr.N + p.kernel->bn - 1) / p.kernel->bn;
   s->batch = pr.batch;
@@ -430,8 +473,8 @@ void build_sched(const Plan& p, const Problem& pr, int workers, SchedParams* s) 
 
 WorkspaceLayout workspace_layout(const Plan& p, const Problem& pr, const SchedParams& s) {
   WorkspaceLayout w{};
-  const int block_m = kCtaRows * (p.pair ? 2 : 1);
-  w.flag_bytes = s.mode == kStreamK ? align_up(static_cast<size_t>(sched_num_slots(s)) * 8 * sizeof(unsigned long long), 256) : 0;
+  const int block_m = p.kernel->block_m;
+  w.flag_bytes = s.mode == kStreamK ? align_up(static_cast<size_t>(sched_num_slots(s)) * 16 * sizeof(unsigned long long), 256) : 0;
   w.partial_bytes =
       align_up(static_cast<size_t>(sched_num_slots(s)) * block_m * p.kernel->bn * sizeof(float), 256);
   w.repitch = needs_repitch(pr);
@@ -495,8 +538,14 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
     pr.strideB = strideA;
   }
 
+  // C can be written in 16-byte pieces (TMA tiles or vector stores) when its row pitch, base and
+  // batch pitch are 16-byte aligned; otherwise the epilogue falls back to 2-byte stores.
+  const bool c_aligned = (pr.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(pr.C) & 15u) == 0) &&
+                         (pr.batch == 1 || pr.strideC % 8 == 0);
+  const int store_mode = !c_aligned ? kStoreScalar : (plan.store_tma ? kStoreTma : kStoreVector);
+  const int epi_bytes = store_mode == kStoreTma ? plan.kernel->epi_bytes : 0;
   const int a_rows = a_rows_for(plan, pr.M);
-  rc = fit_stages(&plan, a_rows);
+  rc = fit_stages(&plan, a_rows, epi_bytes);
   if (rc != B200_OK) return rc;
 
   std::lock_guard<std::mutex> lock(g_mutex);
@@ -545,9 +594,7 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
     b_bstride = static_cast<long long>(pr.N) * ws.k_pitch;
   }
 
-  // C can be written by TMA when its row pitch, base and batch pitch are 16-byte aligned.
-  const bool c_tma = (pr.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(pr.C) & 15u) == 0) &&
-                     (pr.batch == 1 || pr.strideC % 8 == 0);
+  const bool c_tma = store_mode == kStoreTma;
 
   CUtensorMap map_a, map_b, map_c;
   rc = make_tensor_map(&map_a, a_src, pr.K, pr.M, pr.batch, a_pitch * 2, a_bstride * 2, kBlockK, a_rows);
@@ -568,7 +615,8 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   args.K = pr.K;
   args.batch = pr.batch;
   args.stages = plan.stages;
-  args.c_direct = c_tma ? 0 : 1;
+  args.store_mode = store_mode;
+  args.epi_bytes = epi_bytes;
   args.C = static_cast<__nv_bfloat16*>(pr.C);
   args.ldc = pr.N;
   args.c_batch_stride = pr.strideC;
@@ -577,6 +625,13 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
                      ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ws.flag_bytes)
                      : nullptr;
   args.epoch = next_epoch();
+  args.profile = (g_profile != nullptr &&
+                  g_profile_bytes >= static_cast<size_t>(args.sched.num_workers) * (plan.pair ? 2 : 1) *
+                                         kProfileSlots * sizeof(long long))
+                     ? g_profile
+                     : nullptr;
+  args.debug_skip_store = env_int("B200_GEMM_DEBUG_SKIP_STORE", 0);
+  args.l2_hints = env_int("B200_GEMM_L2_HINTS", 0);
   args.a_rows = a_rows;
   args.a_stage_bytes = a_rows * kBlockK * 2;
   args.alpha = alpha;
@@ -587,7 +642,7 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   cudaLaunchConfig_t lc = {};
   const int ctas = args.sched.num_workers * (plan.pair ? 2 : 1);
   lc.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
-  lc.blockDim = dim3(kNumThreads, 1, 1);
+  lc.blockDim = dim3(static_cast<unsigned>(plan.kernel->threads), 1, 1);
   lc.dynamicSmemBytes = static_cast<size_t>(plan.smem);
   lc.stream = stream;
   cudaLaunchAttribute attr;
@@ -597,10 +652,11 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   attr.val.clusterDim.z = 1;
   lc.attrs = &attr;
   lc.numAttrs = 1;
-  B200_CUDA_TRY(cudaLaunchKernelEx(&lc, plan.kernel->fn, map_a, map_b, map_c, args));
+  B200_CUDA_TRY(cudaLaunchKernelEx(&lc, args.profile ? plan.kernel->fn_traced : plan.kernel->fn, map_a, map_b,
+                                   map_c, args));
 
   if (args.sched.mode == kSplitK && sched_num_slots(args.sched) > 0) {
-    const int block_m = kCtaRows * (plan.pair ? 2 : 1);
+    const int block_m = plan.kernel->block_m;
     const int blocks = args.sched.num_tiles < st->sm_count * 4 ? args.sched.num_tiles : st->sm_count * 4;
     fixup_kernel<<<blocks, 256, 0, stream>>>(args, block_m, plan.kernel->bn);
     B200_CUDA_TRY(cudaGetLastError());
@@ -688,7 +744,8 @@ int b200_gemm_default_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg) {
   Plan plan;
   int rc = resolve_plan(*cfg, &plan);
   if (rc != B200_OK) return rc;
-  rc = fit_stages(&plan, a_rows_for(plan, M));
+  rc = fit_stages(&plan, a_rows_for(plan, M),
+                  (N % 8 == 0 && plan.store_tma) ? plan.kernel->epi_bytes : 0);
   if (rc != B200_OK) return rc;
   cfg->stages = plan.stages;
   return B200_OK;
@@ -811,6 +868,13 @@ int b200_gemm_last_device_status(unsigned int out[4]) {
     B200_CUDA_TRY(cudaMemset(st->status, 0, sizeof(unsigned int) * 4));
     return B200_ERR_DEVICE_TIMEOUT;
   }
+  return B200_OK;
+}
+
+int b200_gemm_set_profile_buffer(void* buffer, size_t bytes) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_profile = static_cast<long long*>(buffer);
+  g_profile_bytes = buffer ? bytes : 0;
   return B200_OK;
 }
 

@@ -7,7 +7,8 @@
 //
 //   warp 0      TMA producer   one lane streams A/B K-tiles into a shared-memory ring
 //   warp 1      MMA issuer     one lane issues tcgen05.mma; owns tensor-memory alloc/dealloc
-//   warps 2-5   epilogue       tcgen05.ld -> bf16 -> swizzled smem -> TMA store (one slab/warp)
+//   warps 2-5   epilogue       tcgen05.ld -> bf16 -> either swizzled smem -> TMA store, or
+//   (2-9 if MT = 2)            16-byte global stores straight from registers
 //
 // Barriers (all mbarriers in shared memory, every wait bounded):
 //   full[s]       TMA bytes of stage s have landed           (producer -> MMA issuer)
@@ -22,6 +23,12 @@
 // a 256 x BN tile, each CTA stages its own 128 rows of A and BN/2 rows of B with plain (unicast)
 // TMA loads that complete on the leader CTA's full[s]; the leader alone issues MMAs and signals
 // empty[s] / tmem_full[a] in both CTAs with one commit.
+//
+// MT = 2 gives every CTA two 128-row sub-tiles of A per K-tile (a 256 x BN accumulator per CTA,
+// 512 x BN per pair): the B tile is then reused by twice as many MMAs per byte loaded, which cuts
+// L2 -> shared-memory traffic per FLOP by a quarter. With BN = 256 the two accumulators fill all
+// 512 tensor-memory columns, so there is one accumulator buffer and the epilogue of a tile is not
+// hidden behind the next tile's main loop.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -35,13 +42,9 @@ namespace b200 {
 static constexpr int kBlockK = 64;          // one 128-byte swizzle row of 16-bit elements
 static constexpr int kUmmaK = 16;           // K of one tcgen05.mma (16-bit inputs)
 static constexpr int kCtaRows = 128;        // accumulator rows (TMEM lanes) per CTA
-static constexpr int kNumThreads = 192;     // 6 warps
-static constexpr int kEpiWarps = 4;
-static constexpr int kAccStages = 2;
 static constexpr int kMaxStages = 12;
 static constexpr int kEpiChunkCols = 64;    // columns per TMA store (128 bytes of bf16)
 static constexpr int kEpiSlabBytes = 32 * kEpiChunkCols * 2;       // one warp, one buffer: 4 KB
-static constexpr int kEpiBytes = kEpiWarps * 2 * kEpiSlabBytes;    // 32 KB
 static constexpr int kBarrierBytes = 256;
 
 // Device status codes written to the status word when a bounded wait gives up.
@@ -55,17 +58,43 @@ enum DeviceStatus : unsigned int {
   kStatusSelfTestTimeout = 9,   // the bounded-wait self-test (an mbarrier nothing arrives on)
 };
 
+// Per-CTA cycle counters written when GemmArgs::profile is set: where each role spent its time.
+// (The reference passes a debug buffer "DB" to runKernel for the same purpose but its kernel never
+// writes it, matmul_h100_optimal.cu:132-139,167-198.)
+enum ProfileSlot : int {
+  kProfTotal = 0,          // kernel entry to exit (thread 0)
+  kProfProducerWait = 1,   // TMA producer waiting for a free stage
+  kProfMmaWaitFull = 2,    // MMA issuer waiting for operands
+  kProfMmaWaitTmem = 3,    // MMA issuer waiting for an accumulator buffer
+  kProfEpiWaitFull = 4,    // first epilogue warp waiting for a finished accumulator
+  kProfEpiDrain = 5,       // first epilogue warp: accumulator ready -> buffer handed back
+  kProfEpiBusy = 6,        // first epilogue warp: accumulator ready -> tile's stores issued
+  kProfTiles = 7,          // segments processed
+  kProfileSlots = 8
+};
+
+enum StoreMode : int {
+  kStoreTma = 0,     // staging slab in shared memory, then a TMA tile store
+  kStoreVector = 1,  // 16-byte global stores from registers (needs 16-byte aligned rows of C)
+  kStoreScalar = 2,  // predicated 2-byte stores (any alignment)
+};
+
 struct GemmArgs {
   int M, N, K, batch;
   SchedParams sched;
   int stages;
-  int c_direct;               // 1: write C with predicated global stores instead of TMA
+  int store_mode;             // StoreMode: how the epilogue writes C
+  int epi_bytes;              // shared memory reserved for TMA-store staging (0 unless kStoreTma)
   __nv_bfloat16* C;           // used when c_direct
   long long ldc;              // elements between rows of C
   long long c_batch_stride;   // elements between batches of C
   float* partial;             // fp32 slots for split-K / stream-K partial tiles
-  unsigned long long* flags;  // stream-K: 8 words per slot (CTA rank x TMEM quadrant), set to `epoch`
+  unsigned long long* flags;  // stream-K: 16 words per slot (CTA rank x epilogue warp), set to `epoch`
   unsigned long long epoch;   // value that marks a slot as written by THIS launch
+  int l2_hints;               // 0: none; 1: keep the band operand, stream the other; 2: keep only;
+                              // 3: stream only (the band operand is A for raster 0, B for raster 1)
+  int debug_skip_store;       // measurement only: read the accumulator, write nothing
+  long long* profile;         // optional: kProfileSlots cycle counters per CTA (see ProfileSlot)
   int a_rows;                 // rows of A staged per CTA and K-tile (128, or fewer when M < 128)
   int a_stage_bytes;          // a_rows * 128
   float alpha, beta;
@@ -73,24 +102,35 @@ struct GemmArgs {
   unsigned int* status;       // 4 words: code, block, tile, detail
 };
 
-template <int BN, int PAIR>
+template <int BN, int PAIR, int MT>
 struct KernelTraits {
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN must be 64, 128, 192 or 256");
+  static_assert(MT == 1 || MT == 2, "one or two 128-row sub-tiles of A per CTA");
   static constexpr int kCtaGroup = PAIR ? 2 : 1;
-  static constexpr int kBlockM = kCtaRows * kCtaGroup;
+  static constexpr int kUmmaM = kCtaRows * kCtaGroup;         // rows of one tcgen05.mma
+  static constexpr int kCtaM = kCtaRows * MT;                 // rows of C per CTA
+  static constexpr int kBlockM = kCtaM * kCtaGroup;           // rows of C per worker tile
   static constexpr int kBRowsCta = BN / kCtaGroup;
-  static constexpr int kABytes = kCtaRows * kBlockK * 2;
+  static constexpr int kABytes = kCtaM * kBlockK * 2;         // with a full A tile
   static constexpr int kBBytes = kBRowsCta * kBlockK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;  // with a full 128-row A tile
-  static constexpr int kTmemCols = (kAccStages * BN <= 32)    ? 32
-                                   : (kAccStages * BN <= 64)  ? 64
-                                   : (kAccStages * BN <= 128) ? 128
-                                   : (kAccStages * BN <= 256) ? 256
-                                                              : 512;
-  static constexpr uint32_t kIdescBf16 = make_instr_desc(kBlockM, BN, InFormat::BF16);
-  static constexpr uint32_t kIdescF16 = make_instr_desc(kBlockM, BN, InFormat::F16);
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kChunks = MT * BN / kEpiChunkCols;     // 64-column chunks of a CTA's accumulator
+  static constexpr int kEpiWarps = 4 * MT;                    // one per TMEM lane quadrant and sub-tile
+  static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  static constexpr int kSlabsPerWarp = 2 / MT;                // TMA-store staging slabs per warp
+  static constexpr int kEpiBytes = kEpiWarps * kSlabsPerWarp * kEpiSlabBytes;  // 32 KB
+  static constexpr int kAccCols = MT * BN;                    // TMEM columns of one accumulator buffer
+  static constexpr int kAccStages = (2 * kAccCols <= 512) ? 2 : 1;
+  static constexpr int kTmemCols = (kAccStages * kAccCols <= 32)    ? 32
+                                   : (kAccStages * kAccCols <= 64)  ? 64
+                                   : (kAccStages * kAccCols <= 128) ? 128
+                                   : (kAccStages * kAccCols <= 256) ? 256
+                                                                    : 512;
+  static_assert(kAccStages * kAccCols <= 512, "accumulators exceed tensor memory");
+  static constexpr uint32_t kIdescBf16 = make_instr_desc(kUmmaM, BN, InFormat::BF16);
+  static constexpr uint32_t kIdescF16 = make_instr_desc(kUmmaM, BN, InFormat::F16);
   static constexpr int smem_bytes(int stages) {
-    return 1024 + stages * kStageBytes + kEpiBytes + kBarrierBytes;
+    return 1024 + stages * kStageBytes + kEpiBytes + kBarrierBytes;  // full-height A tile
   }
   static constexpr int max_stages() {
     int s = (232448 - 1024 - kEpiBytes - kBarrierBytes) / kStageBytes;
@@ -132,12 +172,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int BN, int PAIR>
-__global__ void __launch_bounds__(kNumThreads, 1)
+template <int BN, int PAIR, int MT, int PROF>
+__global__ void __launch_bounds__((KernelTraits<BN, PAIR, MT>::kThreads), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmArgs args) {
-  using T = KernelTraits<BN, PAIR>;
+  using T = KernelTraits<BN, PAIR, MT>;
   constexpr int G = T::kCtaGroup;
+  constexpr int kAccStages = T::kAccStages;
   extern __shared__ uint8_t smem_raw[];
 
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x) / 32, 0);
@@ -145,6 +186,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const uint32_t cta_rank = PAIR ? ptx::cluster_ctarank() : 0u;
   const int worker = PAIR ? static_cast<int>(ptx::cluster_id_x()) : static_cast<int>(blockIdx.x);
 
+  // Tracing is a compile-time variant: even a never-taken branch around the cycle-counter reads
+  // in the wait loops slows the main loop measurably.
+  constexpr bool prof = PROF != 0;
+  const long long t_kernel = prof ? clock64() : 0;
+  long long* prof_out = prof ? args.profile + static_cast<long long>(blockIdx.x) * kProfileSlots : nullptr;
   const int stages = args.stages;
   // A stage holds a_rows x 64 of A followed by the B tile. With fewer than 128 rows of A staged
   // (M < 128) the MMA still reads 128 rows: the extra rows are whatever follows in shared
@@ -152,19 +198,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const uint32_t stage_bytes = static_cast<uint32_t>(args.a_stage_bytes) + T::kBBytes;
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t epi_base = smem_base + static_cast<uint32_t>(stages) * stage_bytes;
-  const uint32_t bar_base = epi_base + kEpiBytes;
+  const uint32_t bar_base = epi_base + static_cast<uint32_t>(args.epi_bytes);
   auto a_addr = [&](int s) { return smem_base + static_cast<uint32_t>(s) * stage_bytes; };
   auto b_addr = [&](int s) { return a_addr(s) + static_cast<uint32_t>(args.a_stage_bytes); };
   auto full_bar = [&](int s) { return bar_base + 8u * static_cast<uint32_t>(s); };
   auto empty_bar = [&](int s) { return bar_base + 8u * static_cast<uint32_t>(kMaxStages + s); };
   auto tmem_full_bar = [&](int a) { return bar_base + 8u * static_cast<uint32_t>(2 * kMaxStages + a); };
   auto tmem_empty_bar = [&](int a) {
-    return bar_base + 8u * static_cast<uint32_t>(2 * kMaxStages + kAccStages + a);
+    return bar_base + 8u * static_cast<uint32_t>(2 * kMaxStages + 2 + a);
   };
-  const uint32_t tmem_ptr_addr = bar_base + 8u * (2 * kMaxStages + 2 * kAccStages);
+  const uint32_t tmem_ptr_addr = bar_base + 8u * (2 * kMaxStages + 4);
   uint8_t* generic_bar = smem_raw + (bar_base - ptx::smem_u32(smem_raw));
   volatile uint32_t* tmem_ptr_slot =
-      reinterpret_cast<volatile uint32_t*>(generic_bar + 8 * (2 * kMaxStages + 2 * kAccStages));
+      reinterpret_cast<volatile uint32_t*>(generic_bar + 8 * (2 * kMaxStages + 4));
   volatile uint32_t* abort_flag = tmem_ptr_slot + 1;
 
   // ---------------------------------------------------------------- set-up
@@ -178,7 +224,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     for (int a = 0; a < kAccStages; ++a) {
       ptx::mbar_init(tmem_full_bar(a), 1);
-      ptx::mbar_init(tmem_empty_bar(a), kEpiWarps * G);
+      ptx::mbar_init(tmem_empty_bar(a), T::kEpiWarps * G);
     }
     *abort_flag = 0u;
     ptx::fence_mbar_init();
@@ -201,36 +247,66 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // ===== TMA producer =====
     if (lane == 0) {
       const uint32_t full_base_leader = PAIR ? ptx::map_to_cta(full_bar(0), 0) : full_bar(0);
+      uint64_t pol_a = ptx::l2_policy_evict_normal(), pol_b = pol_a;
+      if (args.l2_hints) {
+        const uint64_t keep = (args.l2_hints == 3) ? pol_a : ptx::l2_policy_evict_last();
+        const uint64_t stream = (args.l2_hints == 2) ? pol_a : ptx::l2_policy_evict_first();
+        pol_a = args.sched.raster == 0 ? keep : stream;
+        pol_b = args.sched.raster == 0 ? stream : keep;
+      }
       WorkIter it(args.sched, worker);
       Segment seg;
       int stage = 0;
       uint32_t phase = 0;
+      // running addresses of the current stage (kept by addition: the ring is latency-critical)
+      uint32_t a_cur = smem_base, full_cur = full_bar(0), empty_cur = empty_bar(0);
+      uint32_t full_leader_cur = full_base_leader;
+      const uint32_t b_off = static_cast<uint32_t>(args.a_stage_bytes);
       bool ok = true;
+      long long waited = 0;
       while (ok && it.next(seg)) {
         const TileCoord tc = tile_coord(args.sched, seg.tile);
-        const int row_a = tc.m * T::kBlockM + static_cast<int>(cta_rank) * kCtaRows;
+        const int row_a = tc.m * T::kBlockM + static_cast<int>(cta_rank) * T::kCtaM;
         const int row_b = tc.n * BN + static_cast<int>(cta_rank) * T::kBRowsCta;
         for (int kt = seg.k_begin; kt < seg.k_end; ++kt) {
-          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u)) {
+          const long long tw = prof ? clock64() : 0;
+          if (!ptx::mbar_wait(empty_cur, phase ^ 1u)) {
             report_timeout(args, kStatusProducerTimeout, seg.tile, kt, abort_flag);
             ok = false;
             break;
           }
-          if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), stage_bytes * G);
+          if (prof) waited += clock64() - tw;
+          if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_cur, stage_bytes * G);
           if (PAIR) {
-            const uint32_t bar = full_base_leader + 8u * static_cast<uint32_t>(stage);
-            ptx::tma_load_3d_pair(a_addr(stage), &map_a, bar, kt * kBlockK, row_a, tc.b);
-            ptx::tma_load_3d_pair(b_addr(stage), &map_b, bar, kt * kBlockK, row_b, tc.b);
+            if (args.l2_hints) {
+              ptx::tma_load_3d_pair_hint(a_cur, &map_a, full_leader_cur, kt * kBlockK, row_a, tc.b, pol_a);
+              ptx::tma_load_3d_pair_hint(a_cur + b_off, &map_b, full_leader_cur, kt * kBlockK, row_b, tc.b, pol_b);
+            } else {
+              ptx::tma_load_3d_pair(a_cur, &map_a, full_leader_cur, kt * kBlockK, row_a, tc.b);
+              ptx::tma_load_3d_pair(a_cur + b_off, &map_b, full_leader_cur, kt * kBlockK, row_b, tc.b);
+            }
+          } else if (args.l2_hints) {
+            ptx::tma_load_3d_hint(a_cur, &map_a, full_cur, kt * kBlockK, row_a, tc.b, pol_a);
+            ptx::tma_load_3d_hint(a_cur + b_off, &map_b, full_cur, kt * kBlockK, row_b, tc.b, pol_b);
           } else {
-            ptx::tma_load_3d(a_addr(stage), &map_a, full_bar(stage), kt * kBlockK, row_a, tc.b);
-            ptx::tma_load_3d(b_addr(stage), &map_b, full_bar(stage), kt * kBlockK, row_b, tc.b);
+            ptx::tma_load_3d(a_cur, &map_a, full_cur, kt * kBlockK, row_a, tc.b);
+            ptx::tma_load_3d(a_cur + b_off, &map_b, full_cur, kt * kBlockK, row_b, tc.b);
           }
+          a_cur += stage_bytes;
+          full_cur += 8u;
+          empty_cur += 8u;
+          full_leader_cur += 8u;
           if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
+            a_cur = smem_base;
+            full_cur = full_bar(0);
+            empty_cur = empty_bar(0);
+            full_leader_cur = full_base_leader;
           }
         }
       }
+      if (prof) prof_out[kProfProducerWait] = waited;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -242,36 +318,58 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
+      uint32_t full_cur = full_bar(0), empty_cur = empty_bar(0);
+      // operand descriptors of the current stage, advanced by addition
+      const uint64_t desc_stage_step = static_cast<uint64_t>(stage_bytes >> 4);
+      const uint64_t desc_a0 = make_smem_desc_sw128(smem_base);
+      const uint64_t desc_b0 = make_smem_desc_sw128(smem_base + static_cast<uint32_t>(args.a_stage_bytes));
+      uint64_t desc_a_cur = desc_a0, desc_b_cur = desc_b0;
       bool ok = true;
+      long long wait_full = 0, wait_tmem = 0;
       while (ok && it.next(seg)) {
+        const long long tw0 = prof ? clock64() : 0;
         if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u)) {
           report_timeout(args, kStatusMmaTmemTimeout, seg.tile, acc, abort_flag);
           break;
         }
+        if (prof) wait_tmem += clock64() - tw0;
         ptx::tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * T::kAccCols);
         for (int kt = seg.k_begin; kt < seg.k_end; ++kt) {
-          if (!ptx::mbar_wait(full_bar(stage), phase)) {
+          const long long tw1 = prof ? clock64() : 0;
+          if (!ptx::mbar_wait(full_cur, phase)) {
             report_timeout(args, kStatusMmaFullTimeout, seg.tile, kt, abort_flag);
             ok = false;
             break;
           }
+          if (prof) wait_full += clock64() - tw1;
           ptx::tc_fence_after_sync();
-          const uint64_t desc_a = make_smem_desc_sw128(a_addr(stage));
-          const uint64_t desc_b = make_smem_desc_sw128(b_addr(stage));
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            ptx::umma_f16<G>(tmem_d, desc_a + k * kDescKStep, desc_b + k * kDescKStep,
-                             T::kIdescBf16, (kt > seg.k_begin || k > 0) ? 1u : 0u);
+          for (int mt = 0; mt < MT; ++mt) {
+            // sub-tile mt: rows [128*mt, 128*mt + 128) of this CTA's A tile -> columns [BN*mt, ...)
+            const uint64_t desc_a = desc_a_cur + static_cast<uint64_t>(mt * ((kCtaRows * kBlockK * 2) >> 4));
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+              ptx::umma_f16<G>(tmem_d + mt * BN, desc_a + k * kDescKStep, desc_b_cur + k * kDescKStep,
+                               T::kIdescBf16, (kt > seg.k_begin || k > 0) ? 1u : 0u);
+            }
           }
           if (PAIR) {
-            ptx::umma_commit_pair(empty_bar(stage), 3);
+            ptx::umma_commit_pair(empty_cur, 3);
           } else {
-            ptx::umma_commit_1cta(empty_bar(stage));
+            ptx::umma_commit_1cta(empty_cur);
           }
+          desc_a_cur += desc_stage_step;
+          desc_b_cur += desc_stage_step;
+          full_cur += 8u;
+          empty_cur += 8u;
           if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
+            desc_a_cur = desc_a0;
+            desc_b_cur = desc_b0;
+            full_cur = full_bar(0);
+            empty_cur = empty_bar(0);
           }
         }
         if (!ok) break;
@@ -285,115 +383,136 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           acc_phase ^= 1u;
         }
       }
+      if (prof) {
+        prof_out[kProfMmaWaitFull] = wait_full;
+        prof_out[kProfMmaWaitTmem] = wait_tmem;
+      }
     }
     __syncwarp();
   } else {
     // ===== epilogue warps =====
-    const int q = warp & 3;  // TMEM lane quadrant this warp may read
-    const uint32_t slab0 = epi_base + static_cast<uint32_t>(warp - 2) * (2 * kEpiSlabBytes);
+    // Warp e = warp - 2 reads TMEM lane quadrant q = warp % 4 of sub-tile e / 4: rows q*32..q*32+31
+    // of that 128-row sub-tile, 64 columns at a time. The accumulator buffer is handed back to the
+    // MMA issuer right after the warp's last TMEM read; conversion and stores of that last chunk
+    // happen after the hand-back.
+    constexpr int kChunksPerSub = BN / kEpiChunkCols;
+    const int e = warp - 2;
+    const int q = warp & 3;
+    const int mt = e >> 2;
+    const uint32_t slab0 = epi_base + static_cast<uint32_t>(e) * (T::kSlabsPerWarp * kEpiSlabBytes);
     const uint32_t tmem_empty_leader =
         PAIR ? ptx::map_to_cta(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+    // stream-K flag word of this warp inside a slot's 16: (CTA rank, epilogue warp)
+    const int flag_lane = static_cast<int>(cta_rank) * 8 + e;
     WorkIter it(args.sched, worker);
     Segment seg;
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t store_count = 0;
+    const bool prof_epi = prof && warp == 2 && lane == 0;
+    long long epi_wait = 0, epi_drain = 0, epi_busy = 0, epi_tiles = 0;
     while (it.next(seg)) {
+      const long long te0 = prof_epi ? clock64() : 0;
       if (!ptx::mbar_wait(tmem_full_bar(acc), acc_phase)) {
         if (lane == 0) report_timeout(args, kStatusEpilogueTimeout, seg.tile, acc, abort_flag);
         break;
       }
       ptx::tc_fence_after_sync();
+      const long long te1 = prof_epi ? clock64() : 0;
+      if (prof_epi) epi_wait += te1 - te0;
       const TileCoord tc = tile_coord(args.sched, seg.tile);
-      const int tile_row = static_cast<int>(cta_rank) * kCtaRows + q * 32;  // slab row in tile
-      const int m_slab = tc.m * T::kBlockM + tile_row;
+      const int cta_row0 = static_cast<int>(cta_rank) * T::kCtaM;  // this CTA's first row in the tile
       const int n_tile = tc.n * BN;
-      const uint32_t tmem_acc =
-          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
       const bool to_slot = seg.slot >= 0;
-      const int row_in_tile = tile_row + static_cast<int>(lane);
-      const bool row_live = (tc.m * T::kBlockM + row_in_tile) < args.M;
-      const bool rows_live = m_slab < args.M;  // warp-uniform: any live row in this slab
+      const bool plain = !to_slot && !seg.finish;
 
-      // Stream-K finisher: the other workers' partial tiles to add, in K order.
+      // Stream-K finisher: wait for the other workers' partial tiles (added below, in K order).
       int contrib_first = 0, contrib_count = 0;
-      bool contrib_ok = true;
       if (seg.finish) {
         contrib_count = streamk_contributors(args.sched, worker, seg.tile, &contrib_first);
-        if (rows_live) {
-          for (int j = 0; j < contrib_count && contrib_ok; ++j) {
-            const unsigned long long* flag =
-                args.flags + (static_cast<long long>(contrib_first + j) * 2 + cta_rank) * 4 + q;
-            const long long t0 = clock64();
-            while (ptx::ld_acquire_u64(flag) != args.epoch) {
-              if (clock64() - t0 > ptx::kWaitBudgetCycles) {
-                contrib_ok = false;
-                break;
-              }
-              __nanosleep(64);
+        bool ok = true;
+        for (int j = 0; j < contrib_count && ok; ++j) {
+          const unsigned long long* flag =
+              args.flags + static_cast<long long>(contrib_first + j) * 16 + flag_lane;
+          const long long t0 = clock64();
+          while (ptx::ld_acquire_u64(flag) != args.epoch) {
+            if (clock64() - t0 > ptx::kWaitBudgetCycles) {
+              ok = false;
+              break;
             }
+            __nanosleep(64);
           }
-          contrib_ok = __all_sync(0xffffffffu, contrib_ok);
-          if (!contrib_ok && lane == 0) {
-            report_timeout(args, kStatusStreamKTimeout, seg.tile, contrib_first, abort_flag);
-          }
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok && lane == 0) {
+          report_timeout(args, kStatusStreamKTimeout, seg.tile, contrib_first, abort_flag);
         }
       }
 
 #pragma unroll 1
-      for (int c = 0; c < BN / kEpiChunkCols; ++c) {
+      for (int c = 0; c < kChunksPerSub; ++c) {  // 64-column chunks of this warp's sub-tile
+        const int tile_row = cta_row0 + mt * kCtaRows + q * 32;  // this warp's first row in the tile
+        const int m_slab = tc.m * T::kBlockM + tile_row;
+        const int row_in_tile = tile_row + static_cast<int>(lane);
+        const bool row_live = (tc.m * T::kBlockM + row_in_tile) < args.M;
         const int n0 = n_tile + c * kEpiChunkCols;
-        const bool live = rows_live && (to_slot || n0 < args.N);
+        // warp-uniform: does this chunk hold anything that is written out?
+        const bool live = (m_slab < args.M) && (to_slot || n0 < args.N);
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                               static_cast<uint32_t>(acc * T::kAccCols + mt * BN + c * kEpiChunkCols);
         uint32_t v[2][32];
         if (live) {
-          ptx::tmem_ld_32x32b_x32(tmem_acc + static_cast<uint32_t>(c * kEpiChunkCols), v[0]);
-          ptx::tmem_ld_32x32b_x32(tmem_acc + static_cast<uint32_t>(c * kEpiChunkCols + 32), v[1]);
+          ptx::tmem_ld_32x32b_x32(taddr, v[0]);
+          ptx::tmem_ld_32x32b_x32(taddr + 32, v[1]);
           ptx::tmem_ld_wait();
         }
-        if (c == BN / kEpiChunkCols - 1) {
-          // All reads of this accumulator buffer are done: hand it back to the MMA issuer.
+        if (c == kChunksPerSub - 1) {
+          // This warp has read all it needs from the accumulator buffer: hand it back.
           ptx::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) {
             ptx::mbar_arrive_cluster(tmem_empty_leader + 8u * static_cast<uint32_t>(acc));
           }
+          if (prof_epi) epi_drain += clock64() - te1;
         }
         if (!live) continue;
+        if (args.debug_skip_store) continue;
 
-        if (to_slot) {
-          // fp32 partial tile: slot[row][col], row-major, tile-local coordinates; rows >= M are
-          // never read back and are not written.
-          if (row_live) {
-            float* dst = args.partial +
-                         (static_cast<long long>(seg.slot) * T::kBlockM + row_in_tile) * BN +
-                         c * kEpiChunkCols;
+        if (!plain) {
+          if (to_slot) {
+            // fp32 partial tile: slot[row][col], row-major, tile-local coordinates; rows >= M are
+            // never read back and are not written.
+            if (row_live) {
+              float* dst = args.partial +
+                           (static_cast<long long>(seg.slot) * T::kBlockM + row_in_tile) * BN +
+                           c * kEpiChunkCols;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+              for (int h = 0; h < 2; ++h) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 f = make_float4(__uint_as_float(v[h][j]), __uint_as_float(v[h][j + 1]),
-                                       __uint_as_float(v[h][j + 2]), __uint_as_float(v[h][j + 3]));
-                __stcg(reinterpret_cast<float4*>(dst + h * 32 + j), f);
+                for (int j = 0; j < 32; j += 4) {
+                  float4 f = make_float4(__uint_as_float(v[h][j]), __uint_as_float(v[h][j + 1]),
+                                         __uint_as_float(v[h][j + 2]), __uint_as_float(v[h][j + 3]));
+                  __stcg(reinterpret_cast<float4*>(dst + h * 32 + j), f);
+                }
               }
             }
+            continue;
           }
-          continue;
-        }
-
-        if (seg.finish && row_live) {
-          for (int j = 0; j < contrib_count; ++j) {
-            const float* src = args.partial +
-                               (static_cast<long long>(contrib_first + j) * T::kBlockM + row_in_tile) * BN +
-                               c * kEpiChunkCols;
+          if (row_live) {
+            for (int j = 0; j < contrib_count; ++j) {
+              const float* src = args.partial +
+                                 (static_cast<long long>(contrib_first + j) * T::kBlockM + row_in_tile) * BN +
+                                 c * kEpiChunkCols;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+              for (int h = 0; h < 2; ++h) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                const float4 f = __ldcg(reinterpret_cast<const float4*>(src + h * 32 + i));
-                v[h][i + 0] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][i + 0]), f.x));
-                v[h][i + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][i + 1]), f.y));
-                v[h][i + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][i + 2]), f.z));
-                v[h][i + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][i + 3]), f.w));
+                for (int k = 0; k < 32; k += 4) {
+                  const float4 f = __ldcg(reinterpret_cast<const float4*>(src + h * 32 + k));
+                  v[h][k + 0] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][k + 0]), f.x));
+                  v[h][k + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][k + 1]), f.y));
+                  v[h][k + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][k + 2]), f.z));
+                  v[h][k + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][k + 3]), f.w));
+                }
               }
             }
           }
@@ -410,15 +529,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
         }
 
-        if (args.c_direct) {
-          const int m = m_slab + static_cast<int>(lane);
-          if (m < args.M) {
-            __nv_bfloat16* dst = args.C + tc.b * args.c_batch_stride + m * args.ldc + n0;
+        if (args.store_mode != kStoreTma) {
+          if (row_live) {
+            __nv_bfloat16* dst = args.C + tc.b * args.c_batch_stride +
+                                 static_cast<long long>(m_slab + static_cast<int>(lane)) * args.ldc + n0;
+            if (args.store_mode == kStoreVector && n0 + kEpiChunkCols <= args.N) {
+              // 128 contiguous bytes of this lane's row, as eight 16-byte stores
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+              for (int h = 0; h < 2; ++h) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (n0 + h * 32 + j < args.N) dst[h * 32 + j] = __float2bfloat16_rn(__uint_as_float(v[h][j]));
+                for (int j = 0; j < 4; ++j) {
+                  uint4 w;
+                  w.x = pack_bf16(__uint_as_float(v[h][8 * j + 0]), __uint_as_float(v[h][8 * j + 1]));
+                  w.y = pack_bf16(__uint_as_float(v[h][8 * j + 2]), __uint_as_float(v[h][8 * j + 3]));
+                  w.z = pack_bf16(__uint_as_float(v[h][8 * j + 4]), __uint_as_float(v[h][8 * j + 5]));
+                  w.w = pack_bf16(__uint_as_float(v[h][8 * j + 6]), __uint_as_float(v[h][8 * j + 7]));
+                  *reinterpret_cast<uint4*>(dst + h * 32 + j * 8) = w;
+                }
+              }
+            } else {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (n0 + h * 32 + j < args.N) dst[h * 32 + j] = __float2bfloat16_rn(__uint_as_float(v[h][j]));
+                }
               }
             }
           }
@@ -426,16 +561,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
 
         // bf16 -> swizzled staging slab -> TMA store of a 32-row x 64-column box.
-        const uint32_t slab = slab0 + (store_count & 1u) * kEpiSlabBytes;
-        if (lane == 0) ptx::tma_store_wait_read<1>();  // the slab used two stores ago is free
+        const uint32_t slab = slab0 + (store_count & (T::kSlabsPerWarp - 1)) * kEpiSlabBytes;
+        if (lane == 0) ptx::tma_store_wait_read<T::kSlabsPerWarp - 1>();  // the slab's last store has read it
         __syncwarp();
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint32_t chunk = static_cast<uint32_t>(h * 4 + j);
+            const uint32_t chunk16 = static_cast<uint32_t>(h * 4 + j);
             ptx::st_shared_v4(
-                slab + sw128_offset(lane, chunk),
+                slab + sw128_offset(lane, chunk16),
                 pack_bf16(__uint_as_float(v[h][8 * j + 0]), __uint_as_float(v[h][8 * j + 1])),
                 pack_bf16(__uint_as_float(v[h][8 * j + 2]), __uint_as_float(v[h][8 * j + 3])),
                 pack_bf16(__uint_as_float(v[h][8 * j + 4]), __uint_as_float(v[h][8 * j + 5])),
@@ -450,13 +585,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         ++store_count;
       }
+      if (prof_epi) {
+        epi_busy += clock64() - te1;
+        ++epi_tiles;
+      }
       if (to_slot && args.sched.mode == kStreamK) {
-        // Publish this warp's rows of the partial tile: every lane's stores, then the flag.
+        // Publish this warp's part of the partial tile: every lane's stores, then the flag.
         __threadfence();
         __syncwarp();
         if (lane == 0) {
-          ptx::st_release_u64(args.flags + (static_cast<long long>(seg.slot) * 2 + cta_rank) * 4 + q,
-                              args.epoch);
+          ptx::st_release_u64(args.flags + static_cast<long long>(seg.slot) * 16 + flag_lane, args.epoch);
         }
       }
       if (++acc == kAccStages) {
@@ -466,6 +604,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     if (lane == 0) ptx::tma_store_wait<0>();
     __syncwarp();
+    if (prof_epi) {
+      prof_out[kProfEpiWaitFull] = epi_wait;
+      prof_out[kProfEpiDrain] = epi_drain;
+      prof_out[kProfEpiBusy] = epi_busy;
+      prof_out[kProfTiles] = epi_tiles;
+    }
   }
 
   // ---------------------------------------------------------------- teardown
@@ -484,6 +628,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc<G>(tmem_base, T::kTmemCols);
   }
+  if (prof && threadIdx.x == 0) prof_out[kProfTotal] = clock64() - t_kernel;
 }
 
 }  // namespace b200

@@ -50,6 +50,11 @@ typedef enum b200_status {
  *   c_col_major  0: C row-major [M,N] (matmul_h100.cu.jinja:696); 1: column-major, leading
  *             dimension M (matmul_utils.cuh:529,545).
  *   max_ctas  cap on the persistent grid; 0 = every SM.
+ *   epilogue  how C is written: 0 = library default, 1 = bf16 tiles staged in shared memory and
+ *             written with TMA tile stores, 2 = 16-byte global stores straight from registers
+ *             (leaves the staging memory to the operand ring). C rows that are not 16-byte aligned
+ *             are always written with 2-byte stores (the reference's epilogue,
+ *             matmul_h100.cu.jinja:689-698).
  */
 typedef struct b200_gemm_cfg {
   int block_m;
@@ -64,6 +69,7 @@ typedef struct b200_gemm_cfg {
   int group;
   int c_col_major;
   int max_ctas;
+  int epilogue;
 } b200_gemm_cfg;
 
 /* Replaces gpu_gemm<AType,BType,CType,AccumType,CLUSTER_M,CLUSTER_N,BLOCKM,BLOCKN,BLOCKK,STAGES>
@@ -118,6 +124,15 @@ int b200_reference_gpu_gemm_bf16(int M, int N, int K, const void* A, const void*
  * out[2] = tile, out[3] = detail. Returns B200_OK or B200_ERR_DEVICE_TIMEOUT; the word is
  * cleared. (The reference's waits are unbounded, barrier.cuh:47-62.) */
 int b200_gemm_last_device_status(unsigned int out[4]);
+
+/* Optional tracing. While a device buffer of at least 8 * (number of CTAs) 64-bit words is
+ * registered, every GEMM launch runs the tracing build of the kernel (a few percent slower) and
+ * writes eight cycle counters per CTA: [0] total, [1] producer wait, [2] MMA wait for operands,
+ * [3] MMA wait for an accumulator buffer, [4] epilogue wait, [5] accumulator drain, [6] epilogue
+ * busy, [7] tiles ([4]-[7] are those of the first epilogue warp). buffer == NULL switches it off. This is the working version of the debug
+ * buffer `DB` the reference allocates for per-SM load/compute/store cycle sums but never fills
+ * (matmul_h100_optimal.cu:132-139,167-198). */
+int b200_gemm_set_profile_buffer(void* buffer, size_t bytes);
 
 /* Failure-detection self-test: launches a one-block kernel that waits, for at most
  * `budget_cycles` SM cycles (<= 2^31), on an mbarrier nothing arrives on. The wait gives up, the

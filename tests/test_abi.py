@@ -60,9 +60,9 @@ def test_workspace_sizes(lib):
     # split-K: split_k * tiles fp32 tiles
     cfg = C(block_n=128, cluster_m=1, sched=1, split_k=4)
     assert api.workspace_bytes(1, 128, 1024, 4096, cfg) == 4 * 8 * 128 * 128 * 4
-    # stream-K: one slot per worker plus 8 flag words each (148 SMs assumed without a device)
+    # stream-K: one slot per worker plus 16 flag words each (148 SMs assumed without a device)
     cfg = C(block_n=128, cluster_m=1, sched=2)
-    assert api.workspace_bytes(1, 64, 28672, 8192, cfg) == 148 * 128 * 128 * 4 + 148 * 64
+    assert api.workspace_bytes(1, 64, 28672, 8192, cfg) == 148 * 128 * 128 * 4 + 148 * 128
     # invalid sizes / unsupported configurations need nothing and report nothing
     assert api.workspace_bytes(1, 0, 10, 10, None) == 0
     assert api.workspace_bytes(1, 128, 128, 128, C(block_n=100)) == 0
@@ -70,8 +70,8 @@ def test_workspace_sizes(lib):
 
 def test_default_config(lib):
     c = api.default_config(1, 8192, 8192, 8192)
-    assert (c.block_m, c.block_n, c.block_k, c.cluster_m, c.cluster_n) == (128, 256, 64, 2, 1)
-    assert c.stages >= 4
+    assert (c.block_m, c.block_n, c.block_k, c.cluster_m, c.cluster_n) == (256, 256, 64, 2, 1)
+    assert c.stages >= 3
     s = api.default_config(1, 16, 28672, 8192)
     assert s.sched == 2 and s.cluster_m == 1
     with pytest.raises(api.GemmError):

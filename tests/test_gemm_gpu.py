@@ -33,11 +33,17 @@ def cfgs():
     for cm in (1, 2):
         for bn in (64, 128, 192, 256):
             out.append(C(block_n=bn, cluster_m=cm))
+    for cm in (1, 2):
+        for bn in (128, 256):
+            out.append(C(block_m=256, block_n=bn, cluster_m=cm))  # two A sub-tiles per CTA
+    out.append(C(block_n=256, cluster_m=2, epilogue=2))                # vector-store epilogue
+    out.append(C(block_m=256, block_n=256, cluster_m=2, epilogue=2))
+    out.append(C(block_n=64, cluster_m=1, epilogue=2))
     return out
 
 
 def cfg_id(c):
-    return "auto" if c is None else f"bn{c.block_n}-cm{c.cluster_m}-st{c.stages}-s{c.sched}k{c.split_k}-r{c.raster}g{c.group}"
+    return "auto" if c is None else f"bm{c.block_m}-bn{c.block_n}-cm{c.cluster_m}-e{c.epilogue}-st{c.stages}-s{c.sched}k{c.split_k}-r{c.raster}g{c.group}"
 
 
 def run(g, a_bits, b_bits, cfg=None, alpha=1.0, beta=0.0):
@@ -193,7 +199,9 @@ def test_skinny_decode(g, skinny_b, m):
                                     dict(block_n=256, cluster_m=2, sched=1, split_k=5),
                                     dict(block_n=128, cluster_m=1, sched=2),
                                     dict(block_n=256, cluster_m=2, sched=2),
-                                    dict(block_n=192, cluster_m=2, sched=2, max_ctas=20)])
+                                    dict(block_n=192, cluster_m=2, sched=2, max_ctas=20),
+                                    dict(block_m=256, block_n=256, cluster_m=2, sched=2),
+                                    dict(block_m=256, block_n=128, cluster_m=1, sched=1, split_k=2)])
 def test_split_and_stream_k_integer_exact(g, cfg_kw):
     from h100_gemm_b200.api import GemmConfig as C
     M, N, K = 700, 900, 3000
@@ -322,6 +330,28 @@ def test_error_codes(g):
                               ctypes.byref(cfg), None, 0, None) == api.STATUS_WORKSPACE
     # the context is still healthy
     assert g.device_status()[0] == 0
+
+
+def test_cycle_counters(g):
+    """The tracing variant of the kernel fills eight counters per CTA and leaves results unchanged."""
+    import torch
+    from h100_gemm_b200 import api
+    a = util.integer_bits((2048, 1024), 1)
+    b = util.integer_bits((2048, 1024), 2)
+    ref = oracle.cpu_gemm(a, b)
+    prof = torch.zeros(148 * 8, dtype=torch.int64, device="cuda")
+    api.set_profile_buffer(prof)
+    try:
+        traced = run(g, a, b, api.GemmConfig(block_n=256, cluster_m=2))
+    finally:
+        api.set_profile_buffer(None)
+    assert np.array_equal(traced, ref)
+    p = prof.view(148, 8).cpu().numpy()
+    tiles = p[:, api.PROFILE_SLOTS.index("tiles")]
+    assert tiles.sum() == 2 * (2048 // 256) * (2048 // 256)  # both CTAs of a pair count each tile
+    busy = p[tiles > 0]
+    assert (busy[:, 0] > 0).all() and (busy[:, 0] >= busy[:, api.PROFILE_SLOTS.index("epi_busy")]).all()
+    assert np.array_equal(run(g, a, b, api.GemmConfig(block_n=256, cluster_m=2)), ref)
 
 
 def test_bounded_wait_gives_up_and_context_survives(g):
