@@ -301,11 +301,6 @@ int make_tensor_map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t
 // ------------------------------------------------------------------------------------------
 // Configuration
 // ------------------------------------------------------------------------------------------
-int env_int(const char* name, int fallback) {
-  const char* v = std::getenv(name);
-  return v ? std::atoi(v) : fallback;
-}
-
 struct Plan {
   const KernelEntry* kernel;
   int pair;
@@ -317,7 +312,7 @@ struct Plan {
   int group;
   int max_ctas;
   int c_col_major;
-  int store_tma;   // 1: TMA-store epilogue; 0: vector stores from registers
+  int store_mode;  // StoreMode to use when C is 16-byte aligned
 };
 
 // Default configuration from the shape. For M > 128 the candidates are ranked by a small cost
@@ -389,8 +384,9 @@ int resolve_plan(const b200_gemm_cfg& c, Plan* p) {
   p->raster = c.raster ? 1 : 0;
   p->group = c.group > 0 ? c.group : 8;
   if (cm > 2) p->group = p->group * (cm / 2);
-  if (c.epilogue < 0 || c.epilogue > 2) return B200_ERR_INVALID_ARG;
-  p->store_tma = c.epilogue == 0 ? 1 : (c.epilogue == 1 ? 1 : 0);
+  if (c.epilogue < 0 || c.epilogue > 3) return B200_ERR_INVALID_ARG;
+  p->store_mode = c.epilogue == 1 ? kStoreTma : c.epilogue == 2 ? kStoreVector : c.epilogue == 3 ? kStoreStaged
+                                                                                                : kStoreTma;
   p->max_ctas = c.max_ctas;
   p->c_col_major = c.c_col_major ? 1 : 0;
   return B200_OK;
@@ -403,6 +399,14 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 int a_rows_for(const Plan& p, int M) {
   if (p.pair || p.kernel->mt > 1 || M >= kCtaRows) return kCtaRows * p.kernel->mt;
   return (M + 7) / 8 * 8;
+}
+
+// Shared memory the epilogue needs for a store mode: two TMA staging slabs per warp (one when a
+// CTA has eight epilogue warps), or one transpose slab per warp.
+int epi_bytes_for(const Plan& p, int store_mode) {
+  if (store_mode == kStoreTma) return p.kernel->epi_bytes;
+  if (store_mode == kStoreStaged) return 4 * p.kernel->mt * kEpiSlabBytes;
+  return 0;
 }
 
 // Settles the ring depth and the dynamic shared-memory size for a given A tile height.
@@ -542,8 +546,8 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   // batch pitch are 16-byte aligned; otherwise the epilogue falls back to 2-byte stores.
   const bool c_aligned = (pr.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(pr.C) & 15u) == 0) &&
                          (pr.batch == 1 || pr.strideC % 8 == 0);
-  const int store_mode = !c_aligned ? kStoreScalar : (plan.store_tma ? kStoreTma : kStoreVector);
-  const int epi_bytes = store_mode == kStoreTma ? plan.kernel->epi_bytes : 0;
+  const int store_mode = !c_aligned ? kStoreScalar : plan.store_mode;
+  const int epi_bytes = epi_bytes_for(plan, store_mode);
   const int a_rows = a_rows_for(plan, pr.M);
   rc = fit_stages(&plan, a_rows, epi_bytes);
   if (rc != B200_OK) return rc;
@@ -630,8 +634,6 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
                                          kProfileSlots * sizeof(long long))
                      ? g_profile
                      : nullptr;
-  args.debug_skip_store = env_int("B200_GEMM_DEBUG_SKIP_STORE", 0);
-  args.l2_hints = env_int("B200_GEMM_L2_HINTS", 0);
   args.a_rows = a_rows;
   args.a_stage_bytes = a_rows * kBlockK * 2;
   args.alpha = alpha;
@@ -744,8 +746,7 @@ int b200_gemm_default_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg) {
   Plan plan;
   int rc = resolve_plan(*cfg, &plan);
   if (rc != B200_OK) return rc;
-  rc = fit_stages(&plan, a_rows_for(plan, M),
-                  (N % 8 == 0 && plan.store_tma) ? plan.kernel->epi_bytes : 0);
+  rc = fit_stages(&plan, a_rows_for(plan, M), epi_bytes_for(plan, N % 8 == 0 ? plan.store_mode : kStoreScalar));
   if (rc != B200_OK) return rc;
   cfg->stages = plan.stages;
   return B200_OK;

@@ -77,6 +77,7 @@ enum StoreMode : int {
   kStoreTma = 0,     // staging slab in shared memory, then a TMA tile store
   kStoreVector = 1,  // 16-byte global stores from registers (needs 16-byte aligned rows of C)
   kStoreScalar = 2,  // predicated 2-byte stores (any alignment)
+  kStoreStaged = 3,  // transpose through a per-warp shared-memory slab, then coalesced 16-byte stores
 };
 
 struct GemmArgs {
@@ -91,9 +92,6 @@ struct GemmArgs {
   float* partial;             // fp32 slots for split-K / stream-K partial tiles
   unsigned long long* flags;  // stream-K: 16 words per slot (CTA rank x epilogue warp), set to `epoch`
   unsigned long long epoch;   // value that marks a slot as written by THIS launch
-  int l2_hints;               // 0: none; 1: keep the band operand, stream the other; 2: keep only;
-                              // 3: stream only (the band operand is A for raster 0, B for raster 1)
-  int debug_skip_store;       // measurement only: read the accumulator, write nothing
   long long* profile;         // optional: kProfileSlots cycle counters per CTA (see ProfileSlot)
   int a_rows;                 // rows of A staged per CTA and K-tile (128, or fewer when M < 128)
   int a_stage_bytes;          // a_rows * 128
@@ -247,13 +245,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // ===== TMA producer =====
     if (lane == 0) {
       const uint32_t full_base_leader = PAIR ? ptx::map_to_cta(full_bar(0), 0) : full_bar(0);
-      uint64_t pol_a = ptx::l2_policy_evict_normal(), pol_b = pol_a;
-      if (args.l2_hints) {
-        const uint64_t keep = (args.l2_hints == 3) ? pol_a : ptx::l2_policy_evict_last();
-        const uint64_t stream = (args.l2_hints == 2) ? pol_a : ptx::l2_policy_evict_first();
-        pol_a = args.sched.raster == 0 ? keep : stream;
-        pol_b = args.sched.raster == 0 ? stream : keep;
-      }
       WorkIter it(args.sched, worker);
       Segment seg;
       int stage = 0;
@@ -278,16 +269,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           if (prof) waited += clock64() - tw;
           if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_cur, stage_bytes * G);
           if (PAIR) {
-            if (args.l2_hints) {
-              ptx::tma_load_3d_pair_hint(a_cur, &map_a, full_leader_cur, kt * kBlockK, row_a, tc.b, pol_a);
-              ptx::tma_load_3d_pair_hint(a_cur + b_off, &map_b, full_leader_cur, kt * kBlockK, row_b, tc.b, pol_b);
-            } else {
-              ptx::tma_load_3d_pair(a_cur, &map_a, full_leader_cur, kt * kBlockK, row_a, tc.b);
-              ptx::tma_load_3d_pair(a_cur + b_off, &map_b, full_leader_cur, kt * kBlockK, row_b, tc.b);
-            }
-          } else if (args.l2_hints) {
-            ptx::tma_load_3d_hint(a_cur, &map_a, full_cur, kt * kBlockK, row_a, tc.b, pol_a);
-            ptx::tma_load_3d_hint(a_cur + b_off, &map_b, full_cur, kt * kBlockK, row_b, tc.b, pol_b);
+            ptx::tma_load_3d_pair(a_cur, &map_a, full_leader_cur, kt * kBlockK, row_a, tc.b);
+            ptx::tma_load_3d_pair(a_cur + b_off, &map_b, full_leader_cur, kt * kBlockK, row_b, tc.b);
           } else {
             ptx::tma_load_3d(a_cur, &map_a, full_cur, kt * kBlockK, row_a, tc.b);
             ptx::tma_load_3d(a_cur + b_off, &map_b, full_cur, kt * kBlockK, row_b, tc.b);
@@ -399,7 +382,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int e = warp - 2;
     const int q = warp & 3;
     const int mt = e >> 2;
-    const uint32_t slab0 = epi_base + static_cast<uint32_t>(e) * (T::kSlabsPerWarp * kEpiSlabBytes);
+    // TMA mode: kSlabsPerWarp staging slabs per warp; staged-store mode: one transpose slab per warp
+    const uint32_t slab0 =
+        epi_base + static_cast<uint32_t>(e) * (args.store_mode == kStoreTma ? T::kSlabsPerWarp * kEpiSlabBytes
+                                                                             : kEpiSlabBytes);
     const uint32_t tmem_empty_leader =
         PAIR ? ptx::map_to_cta(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
     // stream-K flag word of this warp inside a slot's 16: (CTA rank, epilogue warp)
@@ -476,7 +462,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           if (prof_epi) epi_drain += clock64() - te1;
         }
         if (!live) continue;
-        if (args.debug_skip_store) continue;
 
         if (!plain) {
           if (to_slot) {
@@ -527,6 +512,40 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                   __fadd_rn(__fmul_rn(__uint_as_float(v[h][j]), args.alpha), args.beta));
             }
           }
+        }
+
+        if (args.store_mode == kStoreStaged) {
+          // Each lane holds one row; a row-per-lane store touches 32 lines per instruction. Write
+          // the 32 x 64 block to this warp's slab instead and read it back so that 8 lanes cover
+          // one row: every global store instruction then writes four complete 128-byte lines.
+          const uint32_t slab = slab0;
+          __syncwarp();  // the previous chunk's reads of the slab are done
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              ptx::st_shared_v4(
+                  slab + sw128_offset(lane, static_cast<uint32_t>(h * 4 + j)),
+                  pack_bf16(__uint_as_float(v[h][8 * j + 0]), __uint_as_float(v[h][8 * j + 1])),
+                  pack_bf16(__uint_as_float(v[h][8 * j + 2]), __uint_as_float(v[h][8 * j + 3])),
+                  pack_bf16(__uint_as_float(v[h][8 * j + 4]), __uint_as_float(v[h][8 * j + 5])),
+                  pack_bf16(__uint_as_float(v[h][8 * j + 6]), __uint_as_float(v[h][8 * j + 7])));
+            }
+          }
+          __syncwarp();
+          const uint32_t piece = lane & 7u;  // 16-byte piece of a row
+          const int col = n0 + static_cast<int>(piece) * 8;
+          __nv_bfloat16* base = args.C + tc.b * args.c_batch_stride + col;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t r = (lane >> 3) + 4u * static_cast<uint32_t>(i);
+            const uint4 w = ptx::ld_shared_v4(slab + sw128_offset(r, piece));
+            const int m = m_slab + static_cast<int>(r);
+            if (m < args.M && col < args.N) {
+              *reinterpret_cast<uint4*>(base + static_cast<long long>(m) * args.ldc) = w;
+            }
+          }
+          continue;
         }
 
         if (args.store_mode != kStoreTma) {

@@ -146,41 +146,6 @@ B200_DEVICE void tma_load_3d_pair(uint32_t dst, const void* desc, uint32_t clust
       : "memory");
 }
 
-// L2 eviction-priority policies for loads (created at run time; no encoded constants).
-B200_DEVICE uint64_t l2_policy_evict_last() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-B200_DEVICE uint64_t l2_policy_evict_first() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-B200_DEVICE uint64_t l2_policy_evict_normal() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-
-// The two loads above with an L2 cache-policy operand.
-B200_DEVICE void tma_load_3d_hint(uint32_t dst, const void* desc, uint32_t bar, int x, int y, int z,
-                                  uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-      " [%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
-      : "memory");
-}
-B200_DEVICE void tma_load_3d_pair_hint(uint32_t dst, const void* desc, uint32_t cluster_bar, int x,
-                                       int y, int z, uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-      ".L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(desc)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z), "l"(policy)
-      : "memory");
-}
-
 // Tile store shared -> global (bulk async-group completion).
 B200_DEVICE void tma_store_3d(const void* desc, uint32_t src, int x, int y, int z) {
   asm volatile(
@@ -323,6 +288,15 @@ B200_DEVICE void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
                "r"(d)
                : "memory");
+}
+
+B200_DEVICE uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
 }
 
 }  // namespace ptx

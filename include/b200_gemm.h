@@ -52,7 +52,8 @@ typedef enum b200_status {
  *   max_ctas  cap on the persistent grid; 0 = every SM.
  *   epilogue  how C is written: 0 = library default, 1 = bf16 tiles staged in shared memory and
  *             written with TMA tile stores, 2 = 16-byte global stores straight from registers
- *             (leaves the staging memory to the operand ring). C rows that are not 16-byte aligned
+ *             (leaves the staging memory to the operand ring), 3 = transposed through a small
+ *             shared-memory slab per warp and written with coalesced 16-byte stores. C rows that are not 16-byte aligned
  *             are always written with 2-byte stores (the reference's epilogue,
  *             matmul_h100.cu.jinja:689-698).
  */

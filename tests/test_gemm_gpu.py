@@ -39,6 +39,9 @@ def cfgs():
     out.append(C(block_n=256, cluster_m=2, epilogue=2))                # vector-store epilogue
     out.append(C(block_m=256, block_n=256, cluster_m=2, epilogue=2))
     out.append(C(block_n=64, cluster_m=1, epilogue=2))
+    out.append(C(block_n=256, cluster_m=2, epilogue=3))                # staged coalesced stores
+    out.append(C(block_m=256, block_n=256, cluster_m=2, epilogue=3))
+    out.append(C(block_n=192, cluster_m=1, epilogue=3))
     return out
 
 
