@@ -27,6 +27,7 @@ STATUS_SMEM = 3
 STATUS_WORKSPACE = 4
 STATUS_CUDA = 5
 STATUS_DEVICE_TIMEOUT = 6
+STATUS_STATIC_SCRATCH = 8
 
 
 class GemmError(RuntimeError):
@@ -97,6 +98,9 @@ def library() -> ctypes.CDLL:
         lib.b200_gemm_set_profile_buffer.restype = ci
     lib.b200_gemm_selftest_bounded_wait.argtypes = [ll]
     lib.b200_gemm_selftest_bounded_wait.restype = ci
+    if hasattr(lib, "b200_gemm_bf16_fixed_scratch"):
+        lib.b200_gemm_bf16_fixed_scratch.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf, vp]
+        lib.b200_gemm_bf16_fixed_scratch.restype = ci
     lib.b200_gemm_strerror.argtypes = [ci]
     lib.b200_gemm_strerror.restype = ctypes.c_char_p
     lib.b200_gemm_last_cuda_error.argtypes = []
@@ -186,6 +190,25 @@ def gemm(a, b, out=None, alpha: float = 1.0, beta: float = 0.0, cfg: Optional[Ge
     _check(library().b200_gemm_bf16(M, N, K, a.data_ptr(), b.data_ptr(), out.data_ptr(), alpha, beta,
                                     p, ws.data_ptr() if ws is not None else None, ws_bytes,
                                     _stream_ptr(stream)))
+    return out
+
+
+def gemm_fixed_scratch(a, b, out=None, alpha: float = 1.0, beta: float = 0.0, stream=None):
+    """out[M,N] = a @ b^T for M <= 128 without any device allocation by the library or a workspace
+    from the caller (b200_gemm_bf16_fixed_scratch; see include/b200_gemm.h for who needs this and
+    the limits). `out` must be supplied by callers that themselves may not allocate."""
+    import torch
+    _require_cuda_bf16(a, "a", 2)
+    _require_cuda_bf16(b, "b", 2)
+    M, K = a.shape
+    N, Kb = b.shape
+    if K != Kb:
+        raise GemmError(STATUS_INVALID_ARG, "a and b disagree on K")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    _require_cuda_bf16(out, "out", 2)
+    _check(library().b200_gemm_bf16_fixed_scratch(M, N, K, a.data_ptr(), b.data_ptr(), out.data_ptr(), alpha,
+                                                  beta, _stream_ptr(stream)))
     return out
 
 

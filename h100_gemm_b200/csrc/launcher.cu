@@ -761,6 +761,59 @@ int b200_run_kernel(int M, int N, int K, void* A, void* B, void* C, int* DB) {
   return run_gemm(1, M, N, K, A, 0, B, 0, C, 0, 1.0f, 0.0f, &cfg, nullptr, 0, nullptr);
 }
 
+// ------------------------------------------------------------------------------------------
+// GEMM for callers that may not allocate device memory
+// ------------------------------------------------------------------------------------------
+// Some hosts of this library cannot hand it a workspace: a serving loop that sizes all of its
+// device memory once at start-up and forbids cudaMalloc afterwards (the call synchronises the
+// device and can fail late, under memory pressure), or a plug-in interface that passes operands
+// and nothing else. For them the few-rows stream-K GEMM keeps its partial tiles and flag words in
+// the array below, which is part of the library image: every GPU that loads the library holds
+// these 10 MiB until the process exits.
+//
+// kStaticScratchBytes covers the largest layout the few-rows configuration produces: one
+// 128 x 128 fp32 partial tile and 16 flag words per SM for 148 SMs (9 718 272 bytes).
+static constexpr size_t kStaticScratchBytes = 10u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` only names the symbol; it is not a device address. The address a
+// kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+static void* g_static_scratch_ptr[64] = {};
+static std::mutex g_static_scratch_mutex;
+
+int b200_gemm_bf16_fixed_scratch(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
+                                 float beta, void* stream) {
+  int rc = validate(1, M, N, K, A, B, C);
+  if (rc != B200_OK) return rc;
+  // Only the few-rows shapes (M <= 128) run stream-K by default and need scratch at all; the
+  // re-pitched operand copies that K % 8 != 0 or unaligned A/B would need do not fit the budget.
+  if (M > kCtaRows || K % 8 != 0 || (reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(B) & 15u)) {
+    return B200_ERR_STATIC_SCRATCH;
+  }
+  b200_gemm_cfg cfg = default_cfg(1, M, N, K);
+  if (b200_gemm_workspace_bytes(1, M, N, K, &cfg) > kStaticScratchBytes) return B200_ERR_STATIC_SCRATCH;
+
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return B200_ERR_INVALID_ARG;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      B200_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+      if (p == nullptr) return B200_ERR_CUDA;
+      g_static_scratch_ptr[dev] = p;
+    }
+    scratch = g_static_scratch_ptr[dev];
+  }
+  // Nothing in the array has to start at zero: a flag word counts as set only when it holds this
+  // launch's epoch, which no earlier launch (and not the zero-filled image) can have written.
+  rc = run_gemm(1, M, N, K, A, 0, B, 0, C, 0, alpha, beta, &cfg, scratch, kStaticScratchBytes,
+                static_cast<cudaStream_t>(stream));
+  return rc == B200_ERR_WORKSPACE ? B200_ERR_STATIC_SCRATCH : rc;
+}
+
 int b200_reference_gpu_gemm_bf16(int M, int N, int K, const void* A, const void* B, void* C,
                                  float alpha, float beta, void* stream) {
   int rc = validate(1, M, N, K, A, B, C);
@@ -899,6 +952,9 @@ const char* b200_gemm_strerror(int status) {
     case B200_ERR_WORKSPACE: return "workspace missing or too small";
     case B200_ERR_CUDA: return "CUDA call failed";
     case B200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case B200_ERR_STATIC_SCRATCH:
+      return "shape or alignment outside what the fixed scratch entry point covers (M <= 128, K % 8 == 0, "
+             "16-byte aligned A and B)";
     default: return "unknown status";
   }
 }

@@ -29,7 +29,8 @@ typedef enum b200_status {
   B200_ERR_WORKSPACE = 4,       /* workspace missing or smaller than b200_gemm_workspace_bytes */
   B200_ERR_CUDA = 5,            /* a CUDA runtime/driver call failed (see b200_gemm_last_cuda_error) */
   B200_ERR_DEVICE_TIMEOUT = 6,  /* a bounded wait inside the kernel gave up                 */
-  B200_ERR_ALPHA_BETA = 7       /* reserved                                                 */
+  B200_ERR_ALPHA_BETA = 7,      /* reserved                                                 */
+  B200_ERR_STATIC_SCRATCH = 8   /* b200_gemm_bf16_fixed_scratch: shape needs more than its fixed scratch */
 } b200_status;
 
 /* Tunable surface. The first six fields are the template variables of the reference's
@@ -113,6 +114,23 @@ int b200_run_kernel(int M, int N, int K, void* A, void* B, void* C, int* DB);
 int b200_gemm_bf16_host(int M, int N, int K, const void* hA, const void* hB, void* hC, float alpha,
                         float beta, const b200_gemm_cfg* cfg);
 void b200_gemm_host_release(void);
+
+/* The few-rows GEMM (M <= 128, the decode shapes that run stream-K) for callers that cannot
+ * allocate or pass device memory beyond the operands: a serving loop that fixes its device memory
+ * plan at start-up and bans cudaMalloc afterwards, or a plug-in API with no workspace argument.
+ * This entry point has no counterpart in the reference. It computes exactly what b200_gemm_bf16 does
+ * with cfg == NULL, but keeps the stream-K partial tiles and flags in a 10 MiB array inside the
+ * library image (so every GPU that loads the library holds that memory until exit) and calls no
+ * cudaMalloc/cudaFree itself.
+ *   Limits: M <= 128, K % 8 == 0, A and B 16-byte aligned; anything else returns
+ *     B200_ERR_STATIC_SCRATCH (use b200_gemm_bf16 with a workspace instead).
+ *   First call on a device: looks up the array's device address (cudaGetSymbolAddress) and does
+ *     the library's other one-time set-up; make that first call outside any stream capture.
+ *   Sharing: all calls use the same array and it keeps the previous call's contents (the kernel
+ *     does not depend on them). Two calls whose kernels can overlap on the GPU — different
+ *     streams, or different host threads — race on it: serialise them on one stream. */
+int b200_gemm_bf16_fixed_scratch(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
+                                 float beta, void* stream);
 
 /* Replaces reference_gpu_gemm(GemmParams) — reference.h:49-90: a plain SIMT GEMM (one thread per
  * 4x4 outputs, k ascending, fp32) used as an on-device cross-check for shapes too large for the
