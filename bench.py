@@ -40,9 +40,10 @@ WORKLOADS = {
 }
 HBM_BOUND = {"skinny16", "skinny32", "skinny64", "skinny128"}
 
-# DRAM bytes (read + write) of one gemm_kernel launch at 8192^3, from the ncu capture summarised in
-# profiles/gemm_kernel_square8192.md (1.089 GB read + 0.129 GB written); None where no capture exists.
-NCU_DRAM_BYTES_PER_LAUNCH = {"square8192": 1.218e9}
+# DRAM bytes (read + write) of one gemm_kernel launch, from the ncu captures summarised in
+# profiles/gemm_kernel_square8192.md (822.9 MB read + 120.4 MB written) and
+# profiles/gemm_kernel_skinny16.md (471.3 MB + 5.05 MB); None where no capture exists.
+NCU_DRAM_BYTES_PER_LAUNCH = {"square8192": 9.433e8, "prefill_shard": 9.433e8, "skinny16": 4.763e8}
 
 
 def measured_peaks():
