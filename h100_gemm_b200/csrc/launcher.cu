@@ -320,7 +320,6 @@ struct Plan {
 // memory traffic each tile shape needs per FLOP (larger tiles move fewer bytes, which on a
 // power-limited part buys clock; smaller tiles fill the machine when there are few of them).
 b200_gemm_cfg default_cfg(int batch, int M, int N, int K) {
-  (void)K;
   b200_gemm_cfg c;
   std::memset(&c, 0, sizeof(c));
   c.block_m = 128;
@@ -337,10 +336,11 @@ b200_gemm_cfg default_cfg(int batch, int M, int N, int K) {
   }
   struct Cand {
     int block_m, block_n, cluster_m;
-    double penalty;
+    double penalty;  // time per unit of tile area relative to the best shape (tuner, 8192^3)
   };
   static const Cand cands[] = {
-      {256, 256, 2, 1.00}, {128, 256, 2, 1.06}, {128, 128, 2, 1.15}, {128, 128, 1, 1.28}, {128, 64, 1, 1.45},
+      {256, 256, 2, 1.00}, {256, 256, 1, 1.04}, {128, 256, 2, 1.05}, {256, 128, 1, 1.17},
+      {128, 256, 1, 1.27}, {128, 128, 1, 1.58}, {128, 64, 1, 2.13},
   };
   const int sms = 148;
   double best = 0.0;
@@ -349,7 +349,10 @@ b200_gemm_cfg default_cfg(int batch, int M, int N, int K) {
     const long long tiles = ((M + tile_m - 1) / tile_m) * ((N + k.block_n - 1) / k.block_n) * batch;
     const long long workers = sms / k.cluster_m;
     const long long waves = (tiles + workers - 1) / workers;
-    const double cost = static_cast<double>(waves) * k.block_m * k.block_n * k.penalty;
+    double cost = static_cast<double>(waves) * k.block_m * k.block_n * k.penalty;
+    // A 256-row CTA tile has a single accumulator buffer, so its epilogue (a fixed number of
+    // cycles per tile) is exposed; the penalties above include it for K = 8192.
+    if (k.block_m == 256 && k.block_n == 256) cost *= 1.0 + 0.05 * (8192.0 / (K < 512 ? 512 : K) - 1.0);
     if (best == 0.0 || cost < best) {
       best = cost;
       c.block_m = k.block_m;

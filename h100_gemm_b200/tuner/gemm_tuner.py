@@ -34,12 +34,12 @@ REPO = PKG.parent
 DEFAULT_TEMPLATE = PKG / "bench" / "matmul_b200.cu.jinja"
 
 B200_PARAM_SPACE = {
-    'CLUSTER_M': [1, 2, 4],
+    'CLUSTER_M': [1, 2],
     'CLUSTER_N': [1],
-    'BLOCKM': [128],
+    'BLOCKM': [128, 256],
     'BLOCKN': [64, 128, 192, 256],
     'BLOCKK': [64],
-    'STAGES': [3, 4, 5, 6, 8],
+    'STAGES': [3, 4, 6],
 }
 
 # The reference's space (gemm_tuner.py:17-24); BLOCKM 64/256 and STAGES beyond shared memory
