@@ -352,7 +352,7 @@ b200_gemm_cfg default_cfg(int batch, int M, int N, int K) {
     double cost = static_cast<double>(waves) * k.block_m * k.block_n * k.penalty;
     // A 256-row CTA tile has a single accumulator buffer, so its epilogue (a fixed number of
     // cycles per tile) is exposed; the penalties above include it for K = 8192.
-    if (k.block_m == 256 && k.block_n == 256) cost *= 1.0 + 0.05 * (8192.0 / (K < 512 ? 512 : K) - 1.0);
+    if (k.block_m == 256 && k.block_n == 256) cost *= 1.0 + 0.06 * (8192.0 / (K < 512 ? 512 : K) - 1.0);
     if (best == 0.0 || cost < best) {
       best = cost;
       c.block_m = k.block_m;
