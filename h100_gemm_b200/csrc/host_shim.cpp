@@ -63,9 +63,9 @@ int hs_tile_slots(int tiles_m, int tiles_n, int batch, int k_tiles, int mode, in
   return tile_partial_slots(p, tile, out, cap);
 }
 
-int hs_streamk_contributors(int tiles_m, int tiles_n, int batch, int k_tiles, int workers, int worker,
+int hs_streamk_contributors(int tiles_m, int tiles_n, int batch, int k_tiles, int mode, int workers, int worker,
                             int tile, int* first) {
-  SchedParams p = make(tiles_m, tiles_n, batch, k_tiles, 8, 0, kStreamK, 1, workers);
+  SchedParams p = make(tiles_m, tiles_n, batch, k_tiles, 8, 0, mode, 1, workers);
   return streamk_contributors(p, worker, tile, first);
 }
 

@@ -81,10 +81,11 @@ __global__ void fixup_kernel(GemmArgs args, int block_m, int block_n) {
       const int r = idx / vec_per_row;
       const int c = (idx - r * vec_per_row) * 4;
       if (n0 + c >= args.N) continue;
+      // slots are stored in the epilogue's fragment order (partial_element_offset)
+      const long long off = partial_element_offset(block_n, r, c);
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int s = 0; s < n; ++s) {
-        const float4 p = *reinterpret_cast<const float4*>(
-            args.partial + slots[s] * slot_elems + static_cast<long long>(r) * block_n + c);
+        const float4 p = *reinterpret_cast<const float4*>(args.partial + slots[s] * slot_elems + off);
         acc.x += p.x;
         acc.y += p.y;
         acc.z += p.z;
@@ -349,15 +350,22 @@ b200_gemm_cfg default_cfg(int batch, int M, int N, int K) {
     const long long tiles = ((M + tile_m - 1) / tile_m) * ((N + k.block_n - 1) / k.block_n) * batch;
     const long long workers = sms / k.cluster_m;
     const long long waves = (tiles + workers - 1) / workers;
-    double cost = static_cast<double>(waves) * k.block_m * k.block_n * k.penalty;
+    double exposure = 1.0;
     // A 256-row CTA tile has a single accumulator buffer, so its epilogue (a fixed number of
     // cycles per tile) is exposed; the penalties above include it for K = 8192.
-    if (k.block_m == 256 && k.block_n == 256) cost *= 1.0 + 0.06 * (8192.0 / (K < 512 ? 512 : K) - 1.0);
+    if (k.block_m == 256 && k.block_n == 256) exposure = 1.0 + 0.06 * (8192.0 / (K < 512 ? 512 : K) - 1.0);
+    const double area = static_cast<double>(k.block_m) * k.block_n * k.penalty * exposure;
+    const double cost = static_cast<double>(waves) * area;
+    // (The hybrid schedule — full waves data-parallel, last wave stream-K — is available as
+    // sched = 3 but is not chosen here: measured on 3072^3..6144^3 it does not beat plain
+    // data-parallel tiles, the partial-tile round trip costs about what the shorter wave saves.)
+    const int sched = kDataParallel;
     if (best == 0.0 || cost < best) {
       best = cost;
       c.block_m = k.block_m;
       c.block_n = k.block_n;
       c.cluster_m = k.cluster_m;
+      c.sched = sched;
     }
   }
   return c;
@@ -379,7 +387,7 @@ int resolve_plan(const b200_gemm_cfg& c, Plan* p) {
   if (p->stages > kMaxStages) return B200_ERR_UNSUPPORTED_CFG;
   if (p->stages == 1) return B200_ERR_UNSUPPORTED_CFG;
   p->smem = 0;
-  if (c.sched < 0 || c.sched > 2) return B200_ERR_INVALID_ARG;
+  if (c.sched < 0 || c.sched > 3) return B200_ERR_INVALID_ARG;
   p->mode = c.sched;
   p->split_k = c.split_k <= 1 ? 1 : c.split_k;
   if (p->split_k > 64) return B200_ERR_UNSUPPORTED_CFG;
@@ -471,6 +479,7 @@ void build_sched(const Plan& p, const Problem& pr, int workers, SchedParams* s) 
     s->mode = kDataParallel;
     s->split_k = 1;
   }
+  if (s->mode == kHybrid && s->num_tiles <= workers) s->mode = kDataParallel;  // no full wave to keep whole
   long long units = s->num_tiles;
   if (s->mode == kSplitK) units *= s->split_k;
   if (s->mode == kStreamK) units = sched_total_iters(*s);
@@ -481,7 +490,7 @@ void build_sched(const Plan& p, const Problem& pr, int workers, SchedParams* s) 
 WorkspaceLayout workspace_layout(const Plan& p, const Problem& pr, const SchedParams& s) {
   WorkspaceLayout w{};
   const int block_m = p.kernel->block_m;
-  w.flag_bytes = s.mode == kStreamK ? align_up(static_cast<size_t>(sched_num_slots(s)) * 16 * sizeof(unsigned long long), 256) : 0;
+  w.flag_bytes = (s.mode == kStreamK || s.mode == kHybrid) ? align_up(static_cast<size_t>(sched_num_slots(s)) * 16 * sizeof(unsigned long long), 256) : 0;
   w.partial_bytes =
       align_up(static_cast<size_t>(sched_num_slots(s)) * block_m * p.kernel->bn * sizeof(float), 256);
   w.repitch = needs_repitch(pr);

@@ -165,6 +165,22 @@ __global__ void bounded_wait_selftest_kernel(unsigned int* status, long long bud
   }
 }
 
+// Layout of an fp32 partial tile (split-K / stream-K slot) of block_m x BN elements. The tile is
+// stored as the epilogue warps hold it: a fragment is the 32 rows x 64 columns one warp reads from
+// tensor memory in one step; inside a fragment the order is [16-byte piece (16)][row (32)][4 floats].
+// Returns the offset, in floats, of the fragment that holds `row_in_tile` and 64-column chunk `c`
+// (the row's own position inside the fragment, (row % 32) * 4, and the piece index are added by
+// the caller). Host-compilable so the fix-up kernel and the tests share it.
+template <int BN>
+__host__ __device__ __forceinline__ int partial_fragment_offset(int row_in_tile, int c) {
+  return ((row_in_tile >> 5) * (BN / kEpiChunkCols) + c) * (32 * kEpiChunkCols);
+}
+__host__ __device__ __forceinline__ long long partial_element_offset(int block_n, int row, int col) {
+  const int frag = (row >> 5) * (block_n / kEpiChunkCols) + (col / kEpiChunkCols);
+  const int piece = (col % kEpiChunkCols) / 4;
+  return static_cast<long long>(frag) * (32 * kEpiChunkCols) + piece * 128 + (row & 31) * 4 + (col & 3);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -465,19 +481,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
         if (!plain) {
           if (to_slot) {
-            // fp32 partial tile: slot[row][col], row-major, tile-local coordinates; rows >= M are
-            // never read back and are not written.
+            // fp32 partial tile in FRAGMENT order (see partial_fragment_offset): the 32 lanes of a
+            // warp write consecutive 16-byte pieces, so every store instruction fills four whole
+            // 128-byte lines. Rows >= M are never read back and are not written.
             if (row_live) {
-              float* dst = args.partial +
-                           (static_cast<long long>(seg.slot) * T::kBlockM + row_in_tile) * BN +
-                           c * kEpiChunkCols;
+              float* dst = args.partial + static_cast<long long>(seg.slot) * (T::kBlockM * BN) +
+                           partial_fragment_offset<BN>(row_in_tile, c) + lane * 4;
 #pragma unroll
               for (int h = 0; h < 2; ++h) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
                   float4 f = make_float4(__uint_as_float(v[h][j]), __uint_as_float(v[h][j + 1]),
                                          __uint_as_float(v[h][j + 2]), __uint_as_float(v[h][j + 3]));
-                  __stcg(reinterpret_cast<float4*>(dst + h * 32 + j), f);
+                  __stcg(reinterpret_cast<float4*>(dst + (h * 8 + j / 4) * 128), f);
                 }
               }
             }
@@ -485,14 +501,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
           if (row_live) {
             for (int j = 0; j < contrib_count; ++j) {
-              const float* src = args.partial +
-                                 (static_cast<long long>(contrib_first + j) * T::kBlockM + row_in_tile) * BN +
-                                 c * kEpiChunkCols;
+              const float* src = args.partial + static_cast<long long>(contrib_first + j) * (T::kBlockM * BN) +
+                                 partial_fragment_offset<BN>(row_in_tile, c) + lane * 4;
 #pragma unroll
               for (int h = 0; h < 2; ++h) {
 #pragma unroll
                 for (int k = 0; k < 32; k += 4) {
-                  const float4 f = __ldcg(reinterpret_cast<const float4*>(src + h * 32 + k));
+                  const float4 f = __ldcg(reinterpret_cast<const float4*>(src + (h * 8 + k / 4) * 128));
                   v[h][k + 0] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][k + 0]), f.x));
                   v[h][k + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][k + 1]), f.y));
                   v[h][k + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[h][k + 2]), f.z));
@@ -608,7 +623,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         epi_busy += clock64() - te1;
         ++epi_tiles;
       }
-      if (to_slot && args.sched.mode == kStreamK) {
+      if (to_slot && args.sched.mode != kSplitK) {
         // Publish this warp's part of the partial tile: every lane's stores, then the flag.
         __threadfence();
         __syncwarp();

@@ -7,6 +7,9 @@
 //   mode 1  split-K       : every tile is cut into `split_k` K-slices; partial sums go to slots
 //   mode 2  stream-K      : the tiles x k_tiles iteration space is cut into W equal contiguous
 //                           ranges; a range's first/last tile may be partial
+//   mode 3  hybrid        : the full waves of tiles run data-parallel; only the tiles of the last,
+//                           partly filled wave are cut stream-K style, so every worker finishes at
+//                           the same time without paying for partial tiles on the full waves
 // Partial segments carry a slot index into an fp32 workspace. Split-K slots are summed in slot
 // order by a fix-up pass. Under stream-K a tile cut across workers is finished inside the GEMM
 // kernel: the worker holding the tile's head (k_begin == 0) adds the partial tiles of the workers
@@ -28,7 +31,7 @@
 
 namespace b200 {
 
-enum SchedMode : int { kDataParallel = 0, kSplitK = 1, kStreamK = 2 };
+enum SchedMode : int { kDataParallel = 0, kSplitK = 1, kStreamK = 2, kHybrid = 3 };
 
 struct SchedParams {
   int tiles_m;      // output tiles along M
@@ -84,9 +87,21 @@ B200_SCHED_HD long long sched_total_iters(const SchedParams& p) {
   return static_cast<long long>(p.num_tiles) * p.k_tiles;
 }
 
-// First iteration of worker w's contiguous stream-K range.
+// First tile of the stream-K part: 0 for pure stream-K, the end of the last full wave for hybrid.
+B200_SCHED_HD int streamk_tile_base(const SchedParams& p) {
+  if (p.mode == kStreamK) return 0;
+  if (p.mode == kHybrid) return (p.num_tiles / p.num_workers) * p.num_workers;
+  return p.num_tiles;
+}
+
+// Iterations (tile, k-tile) in the stream-K part.
+B200_SCHED_HD long long streamk_iters(const SchedParams& p) {
+  return static_cast<long long>(p.num_tiles - streamk_tile_base(p)) * p.k_tiles;
+}
+
+// First iteration of worker w's contiguous range in the stream-K part.
 B200_SCHED_HD long long streamk_begin(const SchedParams& p, int w) {
-  return sched_total_iters(p) * w / p.num_workers;
+  return streamk_iters(p) * w / p.num_workers;
 }
 
 // K-range of slice s under split-K.
@@ -97,7 +112,9 @@ B200_SCHED_HD int splitk_begin(const SchedParams& p, int s) {
 // Number of fp32 partial slots the workspace must hold.
 B200_SCHED_HD long long sched_num_slots(const SchedParams& p) {
   if (p.mode == kSplitK) return p.split_k > 1 ? static_cast<long long>(p.split_k) * p.num_tiles : 0;
-  if (p.mode == kStreamK) return p.num_workers;  // one per worker: its first segment
+  if (p.mode == kStreamK || p.mode == kHybrid) {
+    return streamk_iters(p) > 0 ? p.num_workers : 0;  // one per worker: its first stream-K segment
+  }
   return 0;
 }
 
@@ -106,52 +123,55 @@ B200_SCHED_HD long long sched_num_slots(const SchedParams& p) {
 struct WorkIter {
   const SchedParams& p;
   int worker;
-  long long cur;  // mode 0/1: next unit id; mode 2: next iteration
-  long long end;  // mode 2: end of this worker's range
-  long long range_begin;
+  long long cur;       // data-parallel / split-K phase: next unit id
+  long long unit_end;  // data-parallel / split-K phase: end of units
+  long long sk_cur;    // stream-K phase: next iteration
+  long long sk_end;    // stream-K phase: end of this worker's range
+  long long sk_range_begin;
+  int sk_tile_base;
 
   B200_SCHED_HD WorkIter(const SchedParams& params, int w) : p(params), worker(w) {
-    if (p.mode == kStreamK) {
-      cur = streamk_begin(p, w);
-      end = streamk_begin(p, w + 1);
-      range_begin = cur;
-    } else {
-      cur = w;
-      end = static_cast<long long>(p.num_tiles) * (p.mode == kSplitK ? p.split_k : 1);
-      range_begin = 0;
-    }
+    sk_tile_base = streamk_tile_base(p);
+    cur = w;
+    unit_end = p.mode == kSplitK ? static_cast<long long>(p.num_tiles) * p.split_k : sk_tile_base;
+    if (p.mode == kDataParallel) unit_end = p.num_tiles;
+    sk_cur = streamk_begin(p, w);
+    sk_end = streamk_begin(p, w + 1);
+    sk_range_begin = sk_cur;
+    if (p.mode == kDataParallel || p.mode == kSplitK) sk_cur = sk_end = 0;
   }
 
   B200_SCHED_HD bool next(Segment& s) {
-    if (cur >= end) return false;
-    if (p.mode == kDataParallel) {
-      s.tile = static_cast<int>(cur);
-      s.k_begin = 0;
-      s.k_end = p.k_tiles;
-      s.slot = -1;
+    if (cur < unit_end) {
+      if (p.mode == kSplitK) {
+        const int slice = static_cast<int>(cur / p.num_tiles);
+        s.tile = static_cast<int>(cur - static_cast<long long>(slice) * p.num_tiles);
+        s.k_begin = splitk_begin(p, slice);
+        s.k_end = splitk_begin(p, slice + 1);
+        s.slot = p.split_k > 1 ? slice * p.num_tiles + s.tile : -1;
+      } else {
+        s.tile = static_cast<int>(cur);
+        s.k_begin = 0;
+        s.k_end = p.k_tiles;
+        s.slot = -1;
+      }
       s.finish = 0;
       cur += p.num_workers;
-    } else if (p.mode == kSplitK) {
-      const int slice = static_cast<int>(cur / p.num_tiles);
-      s.tile = static_cast<int>(cur - static_cast<long long>(slice) * p.num_tiles);
-      s.k_begin = splitk_begin(p, slice);
-      s.k_end = splitk_begin(p, slice + 1);
-      s.slot = p.split_k > 1 ? slice * p.num_tiles + s.tile : -1;
-      s.finish = 0;
-      cur += p.num_workers;
-    } else {
-      s.tile = static_cast<int>(cur / p.k_tiles);
-      const long long tile_first = static_cast<long long>(s.tile) * p.k_tiles;
-      s.k_begin = static_cast<int>(cur - tile_first);
-      long long stop = tile_first + p.k_tiles;
-      if (stop > end) stop = end;
-      s.k_end = static_cast<int>(stop - tile_first);
-      // A range that starts inside a tile contributes a partial; the range holding the tile's
-      // head finishes it when the tile's tail belongs to other workers.
-      s.slot = s.k_begin > 0 ? worker : -1;
-      s.finish = (s.k_begin == 0 && s.k_end < p.k_tiles) ? 1 : 0;
-      cur = stop;
+      return true;
     }
+    if (sk_cur >= sk_end) return false;
+    const int t = static_cast<int>(sk_cur / p.k_tiles);  // tile index inside the stream-K part
+    const long long tile_first = static_cast<long long>(t) * p.k_tiles;
+    s.tile = sk_tile_base + t;
+    s.k_begin = static_cast<int>(sk_cur - tile_first);
+    long long stop = tile_first + p.k_tiles;
+    if (stop > sk_end) stop = sk_end;
+    s.k_end = static_cast<int>(stop - tile_first);
+    // A range that starts inside a tile contributes a partial; the range holding the tile's head
+    // finishes it when the tile's tail belongs to other workers.
+    s.slot = s.k_begin > 0 ? worker : -1;
+    s.finish = (s.k_begin == 0 && s.k_end < p.k_tiles) ? 1 : 0;
+    sk_cur = stop;
     return true;
   }
 };
@@ -176,7 +196,7 @@ B200_SCHED_HD int tile_partial_slots(const SchedParams& p, int tile, int* slots,
 // They are the consecutive workers after `worker` whose ranges start before the tile ends;
 // worker w's partial lives in slot w. Returns their count; *first = worker + 1.
 B200_SCHED_HD int streamk_contributors(const SchedParams& p, int worker, int tile, int* first) {
-  const long long tile_end = (static_cast<long long>(tile) + 1) * p.k_tiles;
+  const long long tile_end = (static_cast<long long>(tile - streamk_tile_base(p)) + 1) * p.k_tiles;
   *first = worker + 1;
   int n = 0;
   for (int w = worker + 1; w < p.num_workers && streamk_begin(p, w) < tile_end; ++w) ++n;

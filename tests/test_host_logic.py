@@ -71,7 +71,7 @@ CASES = [(4, 4, 1, 16), (32, 32, 1, 128), (1, 224, 1, 128), (3, 5, 2, 9), (1, 1,
 
 
 @pytest.mark.parametrize("tm,tn,batch,kt", CASES)
-@pytest.mark.parametrize("mode,split", [(0, 1), (1, 2), (1, 3), (1, 5), (2, 1)])
+@pytest.mark.parametrize("mode,split", [(0, 1), (1, 2), (1, 3), (1, 5), (2, 1), (3, 1)])
 @pytest.mark.parametrize("workers", [1, 7, 74, 148])
 def test_every_k_iteration_is_visited_exactly_once(shim, tm, tn, batch, kt, mode, split, workers):
     tiles = tm * tn * batch
@@ -79,6 +79,8 @@ def test_every_k_iteration_is_visited_exactly_once(shim, tm, tn, batch, kt, mode
         split = min(split, kt)
         if split <= 1:
             mode, split = 0, 1
+    if mode == 3 and tiles <= workers:
+        mode = 0  # what the launcher does: no full wave to keep whole
     units = tiles * (split if mode == 1 else 1) if mode != 2 else tiles * kt
     workers = min(workers, units)
     visits = defaultdict(int)
@@ -95,10 +97,14 @@ def test_every_k_iteration_is_visited_exactly_once(shim, tm, tn, batch, kt, mode
             full = kb == 0 and ke == kt
             if mode == 0:
                 assert slot < 0 and finish == 0
-            if mode == 2:
-                # partials are contributed only by a worker's first segment, into its own slot;
-                # the holder of the tile's head finishes it
-                assert (slot >= 0) == (kb > 0) and (slot < 0 or (slot == w and i == 0))
+            if mode in (2, 3):
+                # partials are contributed only by a worker's first stream-K segment, into its own
+                # slot; the holder of the tile's head finishes it
+                base = 0 if mode == 2 else (tiles // workers) * workers
+                first_sk = next((j for j, sg in enumerate(segs) if sg[0] >= base), None)
+                assert (slot >= 0) == (kb > 0) and (slot < 0 or (slot == w and i == first_sk))
+                if tile < base:
+                    assert full and i < first_sk if first_sk is not None else full
                 assert finish == (1 if (kb == 0 and ke < kt) else 0)
                 assert not full or (slot < 0 and finish == 0)
             if slot >= 0:
@@ -115,18 +121,19 @@ def test_every_k_iteration_is_visited_exactly_once(shim, tm, tn, batch, kt, mode
             n = shim.hs_tile_slots(tm, tn, batch, kt, mode, split, workers, tile, buf, 64)
             assert n <= 64
             assert [buf[i] for i in range(n)] == [s for _, s in sorted(slots_by_tile[tile])]
-    if mode == 2:
+    if mode in (2, 3):
         # every finisher's contributors are the next workers' first segments and tile the rest of K
+        base = 0 if mode == 2 else (tiles // workers) * workers
         first = ctypes.c_int()
         for w, segs in per_worker.items():
             for tile, kb, ke, slot, finish in segs:
                 if not finish:
                     continue
-                n = shim.hs_streamk_contributors(tm, tn, batch, kt, workers, w, tile, ctypes.byref(first))
+                n = shim.hs_streamk_contributors(tm, tn, batch, kt, mode, workers, w, tile, ctypes.byref(first))
                 assert n >= 1 and first.value == w + 1
                 pos = ke
                 for c in range(first.value, first.value + n):
-                    ctile, ckb, cke, cslot, cfin = per_worker[c][0]
+                    ctile, ckb, cke, cslot, cfin = next(sg for sg in per_worker[c] if sg[0] >= base)
                     assert ctile == tile and ckb == pos and cslot == c and cfin == 0
                     pos = cke
                 assert pos == kt
