@@ -297,6 +297,30 @@ def run_ours(args):
     ms_total = float(t.item())
     ms_step = ms_total / args.steps
 
+    # ---- vendor baselines on the same buffers (reported next to the result, not a target) ----
+    vendor = None
+    if world == 1 and not args.kernel_only:
+        try:
+            from h100_gemm_b200 import baselines
+            vendor = {}
+            for name, fn in (("cublas_gemm_ex", baselines.cublas_gemm), ("cublaslt_matmul", baselines.cublaslt_gemm)):
+                for i in range(args.warmup):
+                    fn(a, bs[i % rot], out=c)
+                torch.cuda.synchronize()
+                v0, v1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                v0.record(stream)
+                for i in range(args.steps):
+                    fn(a, bs[i % rot], out=c)
+                v1.record(stream)
+                torch.cuda.synchronize()
+                v_ms = v0.elapsed_time(v1) / args.steps
+                vendor[name] = {"ms_per_step": v_ms,
+                                "value": (2.0 * (M * K + N * K + M * N) / (v_ms * 1e-3) / 1e9) if hbm
+                                else (2.0 * M * N * K / (v_ms * 1e-3) / 1e12),
+                                "unit": "GB/s" if hbm else "TFLOP/s"}
+        except Exception as exc:  # a missing baselines library must not hide the result
+            vendor = {"error": str(exc)}
+
     # ---- optional: the same step followed by an NCCL all-gather of C, chunked and overlapped ----
     gathered = None
     if world > 1 and args.allgather:
@@ -379,6 +403,8 @@ def run_ours(args):
         }
         if gathered is not None:
             line["with_allgather"] = gathered
+        if vendor is not None:
+            line["vendor_baselines"] = vendor
         if args.kernel_only:
             line["e2e"] = None
         if world == 1 and not args.kernel_only:

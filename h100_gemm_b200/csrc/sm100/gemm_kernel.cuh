@@ -42,10 +42,10 @@ namespace b200 {
 static constexpr int kBlockK = 64;          // one 128-byte swizzle row of 16-bit elements
 static constexpr int kUmmaK = 16;           // K of one tcgen05.mma (16-bit inputs)
 static constexpr int kCtaRows = 128;        // accumulator rows (TMEM lanes) per CTA
-static constexpr int kMaxStages = 12;
+static constexpr int kMaxStages = 24;
 static constexpr int kEpiChunkCols = 64;    // columns per TMA store (128 bytes of bf16)
 static constexpr int kEpiSlabBytes = 32 * kEpiChunkCols * 2;       // one warp, one buffer: 4 KB
-static constexpr int kBarrierBytes = 256;
+static constexpr int kBarrierBytes = 512;
 
 // Device status codes written to the status word when a bounded wait gives up.
 enum DeviceStatus : unsigned int {

@@ -73,7 +73,7 @@ def test_default_config(lib):
     assert (c.block_m, c.block_n, c.block_k, c.cluster_m, c.cluster_n) == (256, 256, 64, 2, 1)
     assert c.stages >= 3
     s = api.default_config(1, 16, 28672, 8192)
-    assert s.sched == 2 and s.cluster_m == 1
+    assert s.sched == 2 and s.cluster_m == 1 and s.stages >= 16
     with pytest.raises(api.GemmError):
         api.default_config(1, 0, 1, 1)
 
