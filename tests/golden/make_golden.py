@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz from the REAL reference oracle.
 
-Run in a container that has a checkout of the reference (default /root/reference):
+Run in a container that has a checkout of the reference (its location is the REFERENCE variable of oracle/Makefile):
 
     make -C oracle ref            # builds oracle/_ref/libref_gemm.so from reference.h, in place
     python tests/golden/make_golden.py
