@@ -77,6 +77,11 @@ def library() -> ctypes.CDLL:
     cfgp = ctypes.POINTER(_Cfg)
     lib.b200_gemm_bf16.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf, cfgp, vp, sz, vp]
     lib.b200_gemm_bf16.restype = ci
+    if hasattr(lib, "b200_gemm_f16"):
+        lib.b200_gemm_f16.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf, cfgp, vp, sz, vp]
+        lib.b200_gemm_f16.restype = ci
+        lib.b200_reference_gpu_gemm_f16.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf, vp]
+        lib.b200_reference_gpu_gemm_f16.restype = ci
     lib.b200_gemm_batched_bf16.argtypes = [ci, ci, ci, ci, vp, ll, vp, ll, vp, ll, cf, cf, cfgp, vp, sz, vp]
     lib.b200_gemm_batched_bf16.restype = ci
     lib.b200_gemm_workspace_bytes.argtypes = [ci, ci, ci, ci, cfgp]
@@ -134,12 +139,13 @@ def _stream_ptr(stream) -> Optional[int]:
     return getattr(stream, "cuda_stream", stream) or None
 
 
-def _require_cuda_bf16(t, name: str, ndim: int):
+def _require_cuda_bf16(t, name: str, ndim: int, dtype=None):
     import torch
+    dtype = dtype or torch.bfloat16
     if not t.is_cuda:
         raise GemmError(STATUS_INVALID_ARG, f"{name} must be a CUDA tensor (no CPU fallback exists)")
-    if t.dtype != torch.bfloat16 or t.dim() != ndim or not t.is_contiguous():
-        raise GemmError(STATUS_INVALID_ARG, f"{name} must be a contiguous {ndim}-D bfloat16 tensor")
+    if t.dtype != dtype or t.dim() != ndim or not t.is_contiguous():
+        raise GemmError(STATUS_INVALID_ARG, f"{name} must be a contiguous {ndim}-D {dtype} tensor")
 
 
 def workspace_bytes(batch: int, M: int, N: int, K: int, cfg: Optional[GemmConfig] = None) -> int:
@@ -172,8 +178,9 @@ def gemm(a, b, out=None, alpha: float = 1.0, beta: float = 0.0, cfg: Optional[Ge
     [N, M] (it holds C^T row-major), as matmulKernel of the reference does (matmul_utils.cuh:529).
     """
     import torch
-    _require_cuda_bf16(a, "a", 2)
-    _require_cuda_bf16(b, "b", 2)
+    dtype = torch.float16 if a.dtype == torch.float16 else torch.bfloat16  # fp16 -> b200_gemm_f16
+    _require_cuda_bf16(a, "a", 2, dtype)
+    _require_cuda_bf16(b, "b", 2, dtype)
     M, K = a.shape
     N, Kb = b.shape
     if K != Kb:
@@ -181,13 +188,14 @@ def gemm(a, b, out=None, alpha: float = 1.0, beta: float = 0.0, cfg: Optional[Ge
     col_major = bool(cfg is not None and cfg.c_col_major)
     shape = (N, M) if col_major else (M, N)
     if out is None:
-        out = torch.empty(shape, dtype=torch.bfloat16, device=a.device)
-    _require_cuda_bf16(out, "out", 2)
+        out = torch.empty(shape, dtype=dtype, device=a.device)
+    _require_cuda_bf16(out, "out", 2, dtype)
     if tuple(out.shape) != shape:
         raise GemmError(STATUS_INVALID_ARG, f"out must have shape {shape}")
     ws, ws_bytes = _workspace(workspace_bytes(1, M, N, K, cfg), workspace, a.device)
     keep, p = _cfg_ptr(cfg)
-    _check(library().b200_gemm_bf16(M, N, K, a.data_ptr(), b.data_ptr(), out.data_ptr(), alpha, beta,
+    fn = library().b200_gemm_f16 if dtype == torch.float16 else library().b200_gemm_bf16
+    _check(fn(M, N, K, a.data_ptr(), b.data_ptr(), out.data_ptr(), alpha, beta,
                                     p, ws.data_ptr() if ws is not None else None, ws_bytes,
                                     _stream_ptr(stream)))
     return out
@@ -252,15 +260,17 @@ def run_kernel(a, b, out=None):
 
 
 def reference_gpu_gemm(a, b, out=None, alpha: float = 1.0, beta: float = 0.0, stream=None):
-    """The slow SIMT cross-check GEMM (reference.h:78-90 semantics), row-major C."""
+    """The slow SIMT cross-check GEMM (reference.h:78-90 semantics), row-major C; bf16 or fp16."""
     import torch
-    _require_cuda_bf16(a, "a", 2)
-    _require_cuda_bf16(b, "b", 2)
+    dtype = torch.float16 if a.dtype == torch.float16 else torch.bfloat16
+    _require_cuda_bf16(a, "a", 2, dtype)
+    _require_cuda_bf16(b, "b", 2, dtype)
     M, K = a.shape
     N = b.shape[0]
     if out is None:
-        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
-    _check(library().b200_reference_gpu_gemm_bf16(M, N, K, a.data_ptr(), b.data_ptr(), out.data_ptr(),
+        out = torch.empty((M, N), dtype=dtype, device=a.device)
+    fn = library().b200_reference_gpu_gemm_f16 if dtype == torch.float16 else library().b200_reference_gpu_gemm_bf16
+    _check(fn(M, N, K, a.data_ptr(), b.data_ptr(), out.data_ptr(),
                                                   alpha, beta, _stream_ptr(stream)))
     return out
 

@@ -10,6 +10,7 @@
 //     hard-coded NUM_SM = 128 (matmul_h100_optimal.cu:40).
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <atomic>
@@ -99,7 +100,11 @@ __global__ void fixup_kernel(GemmArgs args, int block_m, int block_n) {
         if (n0 + c + j < args.N) {
           float x = v[j];
           if (args.scale) x = __fadd_rn(__fmul_rn(x, args.alpha), args.beta);
-          dst[j] = __float2bfloat16_rn(x);
+          if (args.f16) {
+            reinterpret_cast<__half*>(dst)[j] = __float2half_rn(x);
+          } else {
+            dst[j] = __float2bfloat16_rn(x);
+          }
         }
       }
     }
@@ -108,9 +113,14 @@ __global__ void fixup_kernel(GemmArgs args, int block_m, int block_n) {
 
 // Plain SIMT GEMM, the on-device cross-check (semantics of reference.h:49-76: k ascending, fp32
 // accumulate, (bf16)(acc * alpha + beta)); one thread per 4x4 outputs.
-__global__ void naive_gemm_kernel(int M, int N, int K, const __nv_bfloat16* __restrict__ A,
-                                  const __nv_bfloat16* __restrict__ B, __nv_bfloat16* __restrict__ C,
-                                  float alpha, float beta) {
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
+__device__ __forceinline__ void from_float(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
+__device__ __forceinline__ void from_float(__half* p, float x) { *p = __float2half_rn(x); }
+
+template <typename T>
+__global__ void naive_gemm_kernel(int M, int N, int K, const T* __restrict__ A, const T* __restrict__ B,
+                                  T* __restrict__ C, float alpha, float beta) {
   const int n0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
   const int m0 = blockIdx.y * 4;
   if (n0 >= N || m0 >= M) return;
@@ -119,8 +129,8 @@ __global__ void naive_gemm_kernel(int M, int N, int K, const __nv_bfloat16* __re
     float a[4], b[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      a[i] = m0 + i < M ? __bfloat162float(A[static_cast<long long>(m0 + i) * K + k]) : 0.f;
-      b[i] = n0 + i < N ? __bfloat162float(B[static_cast<long long>(n0 + i) * K + k]) : 0.f;
+      a[i] = m0 + i < M ? to_float(A[static_cast<long long>(m0 + i) * K + k]) : 0.f;
+      b[i] = n0 + i < N ? to_float(B[static_cast<long long>(n0 + i) * K + k]) : 0.f;
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -130,8 +140,7 @@ __global__ void naive_gemm_kernel(int M, int N, int K, const __nv_bfloat16* __re
   for (int i = 0; i < 4; ++i)
     for (int j = 0; j < 4; ++j)
       if (m0 + i < M && n0 + j < N)
-        C[static_cast<long long>(m0 + i) * N + n0 + j] =
-            __float2bfloat16_rn(__fadd_rn(__fmul_rn(acc[i][j], alpha), beta));
+        from_float(&C[static_cast<long long>(m0 + i) * N + n0 + j], __fadd_rn(__fmul_rn(acc[i][j], alpha), beta));
 }
 
 // ------------------------------------------------------------------------------------------
@@ -145,6 +154,7 @@ struct KernelEntry {
   int mt;         // 128-row sub-tiles of A per CTA
   KernelFn fn;
   KernelFn fn_traced;  // same kernel with the cycle counters compiled in
+  KernelFn fn_f16;     // same kernel for IEEE fp16 operands and output
   int b_bytes;    // bytes of B staged per CTA and K-tile
   int b_rows_cta;
   int block_m;    // rows of C per worker tile
@@ -155,8 +165,17 @@ struct KernelEntry {
 template <int BN, int PAIR, int MT>
 KernelEntry make_entry() {
   using T = KernelTraits<BN, PAIR, MT>;
-  return KernelEntry{BN,         PAIR,          MT,          &gemm_kernel<BN, PAIR, MT, 0>, &gemm_kernel<BN, PAIR, MT, 1>,
-                     T::kBBytes, T::kBRowsCta, T::kBlockM, T::kThreads,                   T::kEpiBytes};
+  return KernelEntry{BN,
+                     PAIR,
+                     MT,
+                     &gemm_kernel<BN, PAIR, MT, 0, 0>,
+                     &gemm_kernel<BN, PAIR, MT, 1, 0>,
+                     &gemm_kernel<BN, PAIR, MT, 0, 1>,
+                     T::kBBytes,
+                     T::kBRowsCta,
+                     T::kBlockM,
+                     T::kThreads,
+                     T::kEpiBytes};
 }
 
 const KernelEntry* find_kernel(int bn, int pair, int mt) {
@@ -231,6 +250,7 @@ int max_resident_workers(DeviceState& st, const KernelEntry& e, int smem, int* o
   // Opt in to the device maximum once, so a later launch with fewer stages cannot shrink it.
   B200_CUDA_TRY(cudaFuncSetAttribute(e.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
   B200_CUDA_TRY(cudaFuncSetAttribute(e.fn_traced, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+  B200_CUDA_TRY(cudaFuncSetAttribute(e.fn_f16, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
   if (smem > st.smem_optin) return B200_ERR_SMEM;
   int workers = st.sm_count;
   if (e.pair) {
@@ -535,7 +555,7 @@ int validate(int batch, int M, int N, int K, const void* A, const void* B, const
 int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, const void* B,
              long long strideB, void* C, long long strideC, float alpha, float beta,
              const b200_gemm_cfg* user_cfg, void* workspace, size_t workspace_bytes,
-             cudaStream_t stream) {
+             cudaStream_t stream, int f16 = 0) {
   int rc = validate(batch, M, N, K, A, B, C);
   if (rc != B200_OK) return rc;
   b200_gemm_cfg cfg = user_cfg ? *user_cfg : default_cfg(batch, M, N, K);
@@ -634,6 +654,7 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   args.K = pr.K;
   args.batch = pr.batch;
   args.stages = plan.stages;
+  args.f16 = f16;
   args.store_mode = store_mode;
   args.epi_bytes = epi_bytes;
   args.C = static_cast<__nv_bfloat16*>(pr.C);
@@ -669,8 +690,10 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   attr.val.clusterDim.z = 1;
   lc.attrs = &attr;
   lc.numAttrs = 1;
-  B200_CUDA_TRY(cudaLaunchKernelEx(&lc, args.profile ? plan.kernel->fn_traced : plan.kernel->fn, map_a, map_b,
-                                   map_c, args));
+  // (the tracing build exists for bf16 only; fp16 launches are never traced)
+  if (f16) args.profile = nullptr;
+  const KernelFn fn = f16 ? plan.kernel->fn_f16 : (args.profile ? plan.kernel->fn_traced : plan.kernel->fn);
+  B200_CUDA_TRY(cudaLaunchKernelEx(&lc, fn, map_a, map_b, map_c, args));
 
   if (args.sched.mode == kSplitK && sched_num_slots(args.sched) > 0) {
     const int block_m = plan.kernel->block_m;
@@ -727,6 +750,12 @@ int b200_gemm_batched_bf16(int batch, int M, int N, int K, const void* A, long l
   if (cfg != nullptr && cfg->c_col_major && batch > 1) return B200_ERR_UNSUPPORTED_CFG;
   return run_gemm(batch, M, N, K, A, strideA, B, strideB, C, strideC, alpha, beta, cfg, workspace,
                   workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int b200_gemm_f16(int M, int N, int K, const void* A, const void* B, void* C, float alpha, float beta,
+                  const b200_gemm_cfg* cfg, void* workspace, size_t workspace_bytes, void* stream) {
+  return run_gemm(1, M, N, K, A, 0, B, 0, C, 0, alpha, beta, cfg, workspace, workspace_bytes,
+                  static_cast<cudaStream_t>(stream), /*f16=*/1);
 }
 
 size_t b200_gemm_workspace_bytes(int batch, int M, int N, int K, const b200_gemm_cfg* user_cfg) {
@@ -835,9 +864,21 @@ int b200_reference_gpu_gemm_bf16(int M, int N, int K, const void* A, const void*
   if (rc != B200_OK) return rc;
   dim3 block(128, 1);
   dim3 grid((N + 511) / 512, (M + 3) / 4);
-  naive_gemm_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+  naive_gemm_kernel<__nv_bfloat16><<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
       M, N, K, static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(B),
       static_cast<__nv_bfloat16*>(C), alpha, beta);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_reference_gpu_gemm_f16(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
+                                float beta, void* stream) {
+  int rc = validate(1, M, N, K, A, B, C);
+  if (rc != B200_OK) return rc;
+  dim3 block(128, 1);
+  dim3 grid((N + 511) / 512, (M + 3) / 4);
+  naive_gemm_kernel<__half><<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+      M, N, K, static_cast<const __half*>(A), static_cast<const __half*>(B), static_cast<__half*>(C), alpha, beta);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }

@@ -1,5 +1,5 @@
 // The one warp-specialised persistent GEMM kernel for sm_100a:  C[M,N] = A[M,K] * B[N,K]^T,
-// 16-bit inputs, fp32 accumulation in tensor memory, bf16 output.
+// 16-bit inputs (bf16 or fp16), fp32 accumulation in tensor memory, output in the input type.
 //
 // It takes the place of both reference kernels — gpu_gemm_kernel (matmul_h100.cu.jinja:734-925:
 // producer warpgroup + two ping-pong WGMMA consumer warpgroups) and matmulKernel
@@ -84,6 +84,7 @@ struct GemmArgs {
   int M, N, K, batch;
   SchedParams sched;
   int stages;
+  int f16;                    // 0: bf16 inputs and output; 1: IEEE fp16 (selects the F16 kernel; used by fix-up)
   int store_mode;             // StoreMode: how the epilogue writes C
   int epi_bytes;              // shared memory reserved for TMA-store staging (0 unless kStoreTma)
   __nv_bfloat16* C;           // used when c_direct
@@ -181,12 +182,22 @@ __host__ __device__ __forceinline__ long long partial_element_offset(int block_n
   return static_cast<long long>(frag) * (32 * kEpiChunkCols) + piece * 128 + (row & 31) * 4 + (col & 3);
 }
 
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
+// Two fp32 values -> one 32-bit word of two 16-bit outputs (lo in the low half), round to nearest
+// even; F16 selects IEEE half instead of bfloat16. The type is a compile-time choice: the epilogue
+// shares issue slots with the MMA issuer, and a run-time selection (two predicated conversions per
+// word) slowed the double-buffered main loop by 4 % (measured).
+template <int F16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  uint32_t r;
+  if constexpr (F16) {
+    asm("cvt.rn.f16x2.f32 %0, %2, %1;" : "=r"(r) : "f"(lo), "f"(hi));
+  } else {
+    asm("cvt.rn.bf16x2.f32 %0, %2, %1;" : "=r"(r) : "f"(lo), "f"(hi));
+  }
+  return r;
 }
 
-template <int BN, int PAIR, int MT, int PROF>
+template <int BN, int PAIR, int MT, int PROF, int F16>
 __global__ void __launch_bounds__((KernelTraits<BN, PAIR, MT>::kThreads), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmArgs args) {
@@ -318,6 +329,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       int acc = 0;
       uint32_t acc_phase = 0;
       uint32_t full_cur = full_bar(0), empty_cur = empty_bar(0);
+      constexpr uint32_t idesc = F16 ? T::kIdescF16 : T::kIdescBf16;
       // operand descriptors of the current stage, advanced by addition
       const uint64_t desc_stage_step = static_cast<uint64_t>(stage_bytes >> 4);
       const uint64_t desc_a0 = make_smem_desc_sw128(smem_base);
@@ -350,7 +362,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
             for (int k = 0; k < kBlockK / kUmmaK; ++k) {
               ptx::umma_f16<G>(tmem_d + mt * BN, desc_a + k * kDescKStep, desc_b_cur + k * kDescKStep,
-                               T::kIdescBf16, (kt > seg.k_begin || k > 0) ? 1u : 0u);
+                               idesc, (kt > seg.k_begin || k > 0) ? 1u : 0u);
             }
           }
           if (PAIR) {
@@ -541,10 +553,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             for (int j = 0; j < 4; ++j) {
               ptx::st_shared_v4(
                   slab + sw128_offset(lane, static_cast<uint32_t>(h * 4 + j)),
-                  pack_bf16(__uint_as_float(v[h][8 * j + 0]), __uint_as_float(v[h][8 * j + 1])),
-                  pack_bf16(__uint_as_float(v[h][8 * j + 2]), __uint_as_float(v[h][8 * j + 3])),
-                  pack_bf16(__uint_as_float(v[h][8 * j + 4]), __uint_as_float(v[h][8 * j + 5])),
-                  pack_bf16(__uint_as_float(v[h][8 * j + 6]), __uint_as_float(v[h][8 * j + 7])));
+                  pack16<F16>(__uint_as_float(v[h][8 * j + 0]), __uint_as_float(v[h][8 * j + 1])),
+                  pack16<F16>(__uint_as_float(v[h][8 * j + 2]), __uint_as_float(v[h][8 * j + 3])),
+                  pack16<F16>(__uint_as_float(v[h][8 * j + 4]), __uint_as_float(v[h][8 * j + 5])),
+                  pack16<F16>(__uint_as_float(v[h][8 * j + 6]), __uint_as_float(v[h][8 * j + 7])));
             }
           }
           __syncwarp();
@@ -574,10 +586,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   uint4 w;
-                  w.x = pack_bf16(__uint_as_float(v[h][8 * j + 0]), __uint_as_float(v[h][8 * j + 1]));
-                  w.y = pack_bf16(__uint_as_float(v[h][8 * j + 2]), __uint_as_float(v[h][8 * j + 3]));
-                  w.z = pack_bf16(__uint_as_float(v[h][8 * j + 4]), __uint_as_float(v[h][8 * j + 5]));
-                  w.w = pack_bf16(__uint_as_float(v[h][8 * j + 6]), __uint_as_float(v[h][8 * j + 7]));
+                  w.x = pack16<F16>(__uint_as_float(v[h][8 * j + 0]), __uint_as_float(v[h][8 * j + 1]));
+                  w.y = pack16<F16>(__uint_as_float(v[h][8 * j + 2]), __uint_as_float(v[h][8 * j + 3]));
+                  w.z = pack16<F16>(__uint_as_float(v[h][8 * j + 4]), __uint_as_float(v[h][8 * j + 5]));
+                  w.w = pack16<F16>(__uint_as_float(v[h][8 * j + 6]), __uint_as_float(v[h][8 * j + 7]));
                   *reinterpret_cast<uint4*>(dst + h * 32 + j * 8) = w;
                 }
               }
@@ -586,7 +598,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
               for (int h = 0; h < 2; ++h) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                  if (n0 + h * 32 + j < args.N) dst[h * 32 + j] = __float2bfloat16_rn(__uint_as_float(v[h][j]));
+                  if (n0 + h * 32 + j < args.N) {
+                    reinterpret_cast<uint16_t*>(dst)[h * 32 + j] =
+                        static_cast<uint16_t>(pack16<F16>(__uint_as_float(v[h][j]), 0.0f) & 0xFFFFu);
+                  }
                 }
               }
             }
@@ -605,10 +620,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const uint32_t chunk16 = static_cast<uint32_t>(h * 4 + j);
             ptx::st_shared_v4(
                 slab + sw128_offset(lane, chunk16),
-                pack_bf16(__uint_as_float(v[h][8 * j + 0]), __uint_as_float(v[h][8 * j + 1])),
-                pack_bf16(__uint_as_float(v[h][8 * j + 2]), __uint_as_float(v[h][8 * j + 3])),
-                pack_bf16(__uint_as_float(v[h][8 * j + 4]), __uint_as_float(v[h][8 * j + 5])),
-                pack_bf16(__uint_as_float(v[h][8 * j + 6]), __uint_as_float(v[h][8 * j + 7])));
+                pack16<F16>(__uint_as_float(v[h][8 * j + 0]), __uint_as_float(v[h][8 * j + 1])),
+                pack16<F16>(__uint_as_float(v[h][8 * j + 2]), __uint_as_float(v[h][8 * j + 3])),
+                pack16<F16>(__uint_as_float(v[h][8 * j + 4]), __uint_as_float(v[h][8 * j + 5])),
+                pack16<F16>(__uint_as_float(v[h][8 * j + 6]), __uint_as_float(v[h][8 * j + 7])));
           }
         }
         ptx::fence_proxy_async_smem();

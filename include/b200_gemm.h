@@ -86,6 +86,12 @@ int b200_gemm_bf16(int M, int N, int K, const void* A, const void* B, void* C, f
                    float beta, const b200_gemm_cfg* cfg, void* workspace, size_t workspace_bytes,
                    void* stream);
 
+/* The same GEMM for IEEE fp16 inputs and output (fp32 accumulation): the data type of the
+ * reference's tunable template, whose only instantiation is half_t (matmul_h100.cu.jinja:1010-1013,
+ * WgMMA<half_t,half_t,float> at :291-292). Same arguments and rules as b200_gemm_bf16. */
+int b200_gemm_f16(int M, int N, int K, const void* A, const void* B, void* C, float alpha, float beta,
+                  const b200_gemm_cfg* cfg, void* workspace, size_t workspace_bytes, void* stream);
+
 /* `batch` independent GEMMs of one shape; stride* are element distances between consecutive
  * problems. No counterpart function in the reference; it covers the batched configuration its
  * rank-3 tensor maps are built for (tma.cuh:83-181 with TmaDim = 3). */
@@ -138,6 +144,11 @@ int b200_gemm_bf16_fixed_scratch(int M, int N, int K, const void* A, const void*
  * CPU oracle. */
 int b200_reference_gpu_gemm_bf16(int M, int N, int K, const void* A, const void* B, void* C,
                                  float alpha, float beta, void* stream);
+
+/* fp16 counterpart of b200_reference_gpu_gemm_bf16 (reference_gpu_gemm<half_t,...>, the check the
+ * reference's template main runs, matmul_h100.cu.jinja:1043-1044). */
+int b200_reference_gpu_gemm_f16(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
+                                float beta, void* stream);
 
 /* Synchronises the current device and reports the device-side status word: out[0] = 0 when no
  * bounded wait has given up since the last call; otherwise out[0] = role code, out[1] = block,

@@ -9,11 +9,13 @@
 //   get_sm_count(), ceil_div()                              common.h:43-60,67
 //
 // Error behaviour follows the reference's CUDA_CHECK (common.h:29-37): print and exit.
-// Only bf16 is instantiated (the reference's template path is fp16-only, its bf16 path is the
-// fixed-configuration runKernel; this project serves bf16 through both).
+// gpu_gemm and reference_gpu_gemm accept bf16 or half_t operands (the reference's template path is
+// half_t only, its bf16 path is the fixed-configuration runKernel; both types go through both
+// entry points here). Accumulation is float.
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <cstdio>
 #include <cstdlib>
@@ -22,6 +24,7 @@
 #include "b200_gemm.h"
 
 using bf16 = __nv_bfloat16;
+using half_t = __half;  // common.h:27
 
 constexpr int ceil_div(int a, int b) { return (a + (b - 1)) / b; }
 
@@ -60,9 +63,10 @@ inline void b200_check(int status, const char* what) {
 template <class AType, class BType, class CType, class AccumType, int CLUSTER_M, int CLUSTER_N,
           int BLOCKM, int BLOCKN, int BLOCKK, int STAGES>
 void gpu_gemm(GemmParams<AType, BType, CType, AccumType> p, bool apply_alpha_beta = false) {
-  static_assert(std::is_same<AType, bf16>::value && std::is_same<BType, bf16>::value &&
-                    std::is_same<CType, bf16>::value && std::is_same<AccumType, float>::value,
-                "gpu_gemm is built for bf16 inputs and outputs with float accumulation");
+  constexpr bool is_bf16 = std::is_same<AType, bf16>::value;
+  static_assert((is_bf16 || std::is_same<AType, half_t>::value) && std::is_same<BType, AType>::value &&
+                    std::is_same<CType, AType>::value && std::is_same<AccumType, float>::value,
+                "gpu_gemm is built for bf16 or fp16 inputs and outputs with float accumulation");
   b200_gemm_cfg cfg = {};
   cfg.block_m = BLOCKM;
   cfg.block_n = BLOCKN;
@@ -72,14 +76,17 @@ void gpu_gemm(GemmParams<AType, BType, CType, AccumType> p, bool apply_alpha_bet
   cfg.cluster_n = CLUSTER_N;
   const float alpha = apply_alpha_beta ? p.alpha : 1.0f;
   const float beta = apply_alpha_beta ? p.beta : 0.0f;
-  b200_check(b200_gemm_bf16(p.M, p.N, p.K, p.A, p.B, p.C, alpha, beta, &cfg, nullptr, 0, nullptr),
+  b200_check(is_bf16 ? b200_gemm_bf16(p.M, p.N, p.K, p.A, p.B, p.C, alpha, beta, &cfg, nullptr, 0, nullptr)
+                     : b200_gemm_f16(p.M, p.N, p.K, p.A, p.B, p.C, alpha, beta, &cfg, nullptr, 0, nullptr),
              "gpu_gemm");
 }
 
 template <class AType, class BType, class CType, class AccumType>
 void reference_gpu_gemm(GemmParams<AType, BType, CType, AccumType> p) {
-  static_assert(std::is_same<AType, bf16>::value, "bf16 only");
-  b200_check(b200_reference_gpu_gemm_bf16(p.M, p.N, p.K, p.A, p.B, p.C, p.alpha, p.beta, nullptr),
+  constexpr bool is_bf16 = std::is_same<AType, bf16>::value;
+  static_assert(is_bf16 || std::is_same<AType, half_t>::value, "bf16 or fp16");
+  b200_check(is_bf16 ? b200_reference_gpu_gemm_bf16(p.M, p.N, p.K, p.A, p.B, p.C, p.alpha, p.beta, nullptr)
+                     : b200_reference_gpu_gemm_f16(p.M, p.N, p.K, p.A, p.B, p.C, p.alpha, p.beta, nullptr),
              "reference_gpu_gemm");
 }
 

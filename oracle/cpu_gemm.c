@@ -43,6 +43,64 @@ static inline uint16_t f32_to_bf16_rne(float f) {
   return (uint16_t)(u >> 16);
 }
 
+/* IEEE binary16 <-> fp32, as cuda_fp16.h's host path does: widening is exact; narrowing rounds to
+ * nearest even, produces subnormals, overflows to infinity, and maps NaN to 0x7FFF. */
+static inline float f16_to_f32(uint16_t h) {
+  const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1Fu;
+  uint32_t man = h & 0x3FFu;
+  uint32_t u;
+  if (exp == 0) {
+    if (man == 0) {
+      u = sign;
+    } else { /* subnormal: normalise */
+      int e = -1;
+      do {
+        ++e;
+        man <<= 1;
+      } while ((man & 0x400u) == 0);
+      u = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3FFu) << 13);
+    }
+  } else if (exp == 31) {
+    u = sign | 0x7F800000u | (man << 13);
+  } else {
+    u = sign | ((exp + 127 - 15) << 23) | (man << 13);
+  }
+  float f;
+  memcpy(&f, &u, sizeof f);
+  return f;
+}
+
+static inline uint16_t f32_to_f16_rne(float f) {
+  uint32_t u;
+  memcpy(&u, &f, sizeof u);
+  const uint16_t sign = (uint16_t)((u >> 16) & 0x8000u);
+  const uint32_t abs = u & 0x7FFFFFFFu;
+  if (abs > 0x7F800000u) return 0x7FFFu;                    /* NaN */
+  if (abs >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u); /* rounds to >= 65520: infinity */
+  if (abs < 0x33000001u) return sign;                        /* below half the smallest subnormal */
+  int exp = (int)(abs >> 23) - 127;
+  uint32_t man = (abs & 0x7FFFFFu) | 0x800000u;
+  int shift;
+  uint32_t base;
+  if (exp < -14) { /* subnormal result */
+    shift = 13 + (-14 - exp);
+    base = 0;
+  } else {
+    shift = 13;
+    base = (uint32_t)(exp + 15) << 10;
+    man &= 0x7FFFFFu;
+  }
+  uint32_t q = man >> shift;
+  const uint32_t rem = man & ((1u << shift) - 1u);
+  const uint32_t half = 1u << (shift - 1);
+  if (rem > half || (rem == half && (q & 1u))) ++q; /* carries into the exponent correctly */
+  return (uint16_t)(sign | (base + q));
+}
+
+uint16_t oracle_f32_to_f16(float f) { return f32_to_f16_rne(f); }
+float oracle_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
+
 uint16_t oracle_f32_to_bf16(float f) { return f32_to_bf16_rne(f); }
 float oracle_bf16_to_f32(uint16_t h) { return bf16_to_f32(h); }
 
@@ -82,6 +140,31 @@ void oracle_cpu_gemm_bf16_rows(int M, int N, int K, const uint16_t* A, const uin
     }
     free(a_f);
     free(b_f);
+  }
+}
+
+/* reference_cpu_gemm<half_t, half_t, half_t, float>: the instantiation the reference's template
+ * path uses (matmul_h100.cu.jinja:1010-1013). Same loop; only the conversions differ. The product
+ * of two fp16 values has at most 22 significant bits, so it too is exact in fp32. */
+void oracle_cpu_gemm_f16(int M, int N, int K, const uint16_t* A, const uint16_t* B, uint16_t* C,
+                         float alpha, float beta) {
+#pragma omp parallel
+  {
+    float* a_f = (float*)malloc(sizeof(float) * (size_t)K);
+    float* acc = (float*)malloc(sizeof(float) * (size_t)N);
+#pragma omp for schedule(dynamic, 4)
+    for (int i = 0; i < M; ++i) {
+      for (int k = 0; k < K; ++k) a_f[k] = f16_to_f32(A[(size_t)i * K + k]);
+      for (int j = 0; j < N; ++j) {
+        const uint16_t* b = B + (size_t)j * K;
+        float s = 0.0f;
+        for (int k = 0; k < K; ++k) s += a_f[k] * f16_to_f32(b[k]);
+        acc[j] = s;
+      }
+      for (int j = 0; j < N; ++j) C[(size_t)i * N + j] = f32_to_f16_rne(acc[j] * alpha + beta);
+    }
+    free(a_f);
+    free(acc);
   }
 }
 

@@ -36,6 +36,8 @@ def _load_oracle() -> ctypes.CDLL:
         lib.oracle_cpu_gemm_bf16_rows.restype = None
         lib.oracle_cpu_gemm_bf16_sampled_rows.argtypes = [ci, ci, vp, vp, vp, cf, cf, vp, ci]
         lib.oracle_cpu_gemm_bf16_sampled_rows.restype = None
+        lib.oracle_cpu_gemm_f16.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf]
+        lib.oracle_cpu_gemm_f16.restype = None
         lib.oracle_f32_to_bf16.argtypes = [cf]
         lib.oracle_f32_to_bf16.restype = ctypes.c_uint16
         _oracle = lib
@@ -53,6 +55,9 @@ def _load_ref() -> ctypes.CDLL:
         vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
         lib.ref_cpu_gemm_bf16.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf]
         lib.ref_cpu_gemm_bf16.restype = None
+        if hasattr(lib, "ref_cpu_gemm_f16"):
+            lib.ref_cpu_gemm_f16.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf]
+            lib.ref_cpu_gemm_f16.restype = None
         _ref = lib
     return _ref
 
@@ -107,13 +112,43 @@ def reference_cpu_gemm(a: np.ndarray, b: np.ndarray, alpha: float = 1.0, beta: f
     return c
 
 
-def norm_relative_error(c_bits: np.ndarray, ref_bits: np.ndarray, a_bits: np.ndarray, b_bits: np.ndarray) -> float:
+def f32_to_f16_bits(x: np.ndarray) -> np.ndarray:
+    """fp32 -> IEEE half bit patterns (numpy's conversion is round-to-nearest-even)."""
+    return np.ascontiguousarray(x, dtype=np.float32).astype(np.float16).view(np.uint16)
+
+
+def f16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(bits, dtype=np.uint16).view(np.float16).astype(np.float32)
+
+
+def cpu_gemm_f16(a: np.ndarray, b: np.ndarray, alpha: float = 1.0, beta: float = 0.0) -> np.ndarray:
+    """The oracle for fp16 inputs/outputs (reference_cpu_gemm<half_t,half_t,half_t,float>)."""
+    a, b = _check(a, b)
+    M, K = a.shape
+    N = b.shape[0]
+    c = np.empty((M, N), dtype=np.uint16)
+    _load_oracle().oracle_cpu_gemm_f16(M, N, K, a.ctypes.data, b.ctypes.data, c.ctypes.data, alpha, beta)
+    return c
+
+
+def reference_cpu_gemm_f16(a: np.ndarray, b: np.ndarray, alpha: float = 1.0, beta: float = 0.0) -> np.ndarray:
+    a, b = _check(a, b)
+    M, K = a.shape
+    N = b.shape[0]
+    c = np.empty((M, N), dtype=np.uint16)
+    _load_ref().ref_cpu_gemm_f16(M, N, K, a.ctypes.data, b.ctypes.data, c.ctypes.data, alpha, beta)
+    return c
+
+
+def norm_relative_error(c_bits: np.ndarray, ref_bits: np.ndarray, a_bits: np.ndarray, b_bits: np.ndarray,
+                        f16: bool = False) -> float:
     """max_ij |C_ij - R_ij| / (||A_i||_2 * ||B_j||_2): the acceptance metric (bound 1e-2)."""
-    a = bf16_bits_to_f32(a_bits).astype(np.float64)
-    b = bf16_bits_to_f32(b_bits).astype(np.float64)
+    widen = f16_bits_to_f32 if f16 else bf16_bits_to_f32
+    a = widen(a_bits).astype(np.float64)
+    b = widen(b_bits).astype(np.float64)
     na = np.sqrt((a * a).sum(axis=1))
     nb = np.sqrt((b * b).sum(axis=1))
     denom = np.outer(na, nb)
     denom[denom == 0] = 1.0
-    d = np.abs(bf16_bits_to_f32(c_bits).astype(np.float64) - bf16_bits_to_f32(ref_bits).astype(np.float64))
+    d = np.abs(widen(c_bits).astype(np.float64) - widen(ref_bits).astype(np.float64))
     return float((d / denom).max())

@@ -13,6 +13,14 @@
 
 #include "reference.h"
 
+extern "C" void ref_cpu_gemm_f16(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
+                                 float beta) {
+  GemmParams<half_t, half_t, half_t, float> params(M, N, K, static_cast<const half_t*>(A),
+                                                   static_cast<const half_t*>(B), static_cast<half_t*>(C), alpha,
+                                                   beta);
+  reference_cpu_gemm(params);
+}
+
 extern "C" void ref_cpu_gemm_bf16(int M, int N, int K, const void* A, const void* B, void* C,
                                   float alpha, float beta) {
   GemmParams<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16, float> params(

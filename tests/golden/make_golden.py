@@ -45,6 +45,20 @@ def gen(kind, shape, seed):
     return util.normal_bits(shape, seed)
 
 
+F16_CASES = [
+    # fp16 fixtures: the data type of the reference's template path (reference_cpu_gemm<half_t,...>)
+    ("f16_uniform_70x90x300", 70, 90, 300, "uniform", 1.0, 0.0),
+    ("f16_integer_64x96x256", 64, 96, 256, "integer", 1.0, 0.0),
+    ("f16_alphabeta_33x47x129", 33, 47, 129, "uniform", 0.5, 0.25),
+]
+
+
+def gen_f16(kind, shape, seed):
+    rng = np.random.Generator(np.random.Philox(seed))
+    x = rng.integers(-5, 5, size=shape) if kind == "integer" else rng.uniform(-1.0, 1.0, size=shape)
+    return oracle.f32_to_f16_bits(x.astype(np.float32))
+
+
 def sha(a: np.ndarray) -> str:
     return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
 
@@ -55,6 +69,12 @@ def main():
         a = gen(kind, (M, K), 100 + 2 * i)
         b = gen(kind, (N, K), 101 + 2 * i)
         c = oracle.reference_cpu_gemm(a, b, alpha, beta)
+        np.savez_compressed(HERE / f"{name}.npz", a=a, b=b, c=c, alpha=np.float32(alpha), beta=np.float32(beta))
+        print(name, c.shape)
+    for i, (name, M, N, K, kind, alpha, beta) in enumerate(F16_CASES):
+        a = gen_f16(kind, (M, K), 300 + 2 * i)
+        b = gen_f16(kind, (N, K), 301 + 2 * i)
+        c = oracle.reference_cpu_gemm_f16(a, b, alpha, beta)
         np.savez_compressed(HERE / f"{name}.npz", a=a, b=b, c=c, alpha=np.float32(alpha), beta=np.float32(beta))
         print(name, c.shape)
     # Configuration 1: M=N=K=1024, uniform[-1,1], seed 0 (A) and 1 (B).

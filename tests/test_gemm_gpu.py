@@ -85,7 +85,8 @@ def test_config1_full_matrix(g, config1, cfg):
     assert np.mean(diff > 0) < 0.2
 
 
-@pytest.mark.parametrize("path", sorted(p for p in GOLDEN.glob("*.npz") if p.name != "config1_1024.npz"),
+@pytest.mark.parametrize("path", sorted(p for p in GOLDEN.glob("*.npz")
+                                        if p.name != "config1_1024.npz" and not p.name.startswith("f16_")),
                          ids=lambda p: p.stem)
 def test_golden_fixtures(g, path):
     """Small, ragged shapes (K=1, a single row, tails in every dimension, alpha/beta)."""
@@ -282,6 +283,56 @@ def test_batched_32x2048x2048x512(g):
     c = g.gemm_batched(a, b)
     for i in range(5):
         assert np.array_equal(util.to_bits(c[i]), oracle.cpu_gemm(util.to_bits(a[i]), util.to_bits(b[i])))
+
+
+# ------------------------------------------------------------------------------------------------
+# fp16: the data type of the reference's template path (b200_gemm_f16)
+# ------------------------------------------------------------------------------------------------
+def run_f16(g, a_bits, b_bits, cfg=None, alpha=1.0, beta=0.0):
+    out = g.gemm(util.to_device_f16(a_bits), util.to_device_f16(b_bits), cfg=cfg, alpha=alpha, beta=beta)
+    rc, words = g.device_status()
+    assert rc == 0, f"device status {words}"
+    return util.to_bits(out.view(__import__("torch").bfloat16))
+
+
+@pytest.mark.parametrize("path", sorted(GOLDEN.glob("f16_*.npz")), ids=lambda p: p.stem)
+def test_fp16_golden_fixtures(g, path):
+    gold = np.load(path)
+    a, b, ref = gold["a"], gold["b"], gold["c"]
+    for cfg in (None, cfgs()[1], cfgs()[7], cfgs()[11]):
+        c = run_f16(g, a, b, cfg, float(gold["alpha"]), float(gold["beta"]))
+        if "integer" in path.stem:
+            assert np.array_equal(c, ref)
+        else:
+            assert oracle.norm_relative_error(c, ref, a, b, f16=True) <= TOL
+
+
+@pytest.mark.parametrize("cfg", [None] + cfgs()[:12:3] + cfgs()[-3:], ids=cfg_id)
+def test_fp16_parity(g, cfg):
+    from h100_gemm_b200.api import GemmConfig as C
+    M, N, K = 1000, 776, 1544
+    a = util.f16_integer_bits((M, K), 31)
+    b = util.f16_integer_bits((N, K), 32)
+    assert np.array_equal(run_f16(g, a, b, cfg), oracle.cpu_gemm_f16(a, b))
+    a = util.f16_uniform_bits((M, K), 33)
+    b = util.f16_uniform_bits((N, K), 34)
+    ref = oracle.cpu_gemm_f16(a, b)
+    c = run_f16(g, a, b, cfg)
+    # fp16 keeps 11 significant bits: the bound is the acceptance one, the typical error far lower
+    assert oracle.norm_relative_error(c, ref, a, b, f16=True) <= TOL
+    assert np.mean(c != ref) < 0.2
+    # stream-K and split-K finish fp16 tiles too
+    for extra in (C(block_n=128, cluster_m=1, sched=2), C(block_n=128, cluster_m=1, sched=1, split_k=3)):
+        assert oracle.norm_relative_error(run_f16(g, a, b, extra), ref, a, b, f16=True) <= TOL
+
+
+def test_fp16_simt_cross_check(g):
+    import torch
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    a = torch.randint(-5, 5, (2048, 1024), device="cuda", generator=gen).to(torch.float16)
+    b = torch.randint(-5, 5, (1536, 1024), device="cuda", generator=gen).to(torch.float16)
+    assert torch.equal(g.gemm(a, b).view(torch.int16), g.reference_gpu_gemm(a, b).view(torch.int16))
+    assert g.device_status()[0] == 0
 
 
 # ------------------------------------------------------------------------------------------------

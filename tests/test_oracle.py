@@ -16,7 +16,8 @@ import util
 from oracle import oracle
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
-SMALL = sorted(p for p in GOLDEN.glob("*.npz") if p.name != "config1_1024.npz")
+SMALL = sorted(p for p in GOLDEN.glob("*.npz") if p.name != "config1_1024.npz" and not p.name.startswith("f16_"))
+F16 = sorted(GOLDEN.glob("f16_*.npz"))
 
 
 def sha(a):
@@ -28,6 +29,42 @@ def test_oracle_matches_golden(path):
     g = np.load(path)
     c = oracle.cpu_gemm(g["a"], g["b"], float(g["alpha"]), float(g["beta"]))
     assert np.array_equal(c, g["c"])
+
+
+@pytest.mark.parametrize("path", F16, ids=lambda p: p.stem)
+def test_fp16_oracle_matches_golden(path):
+    """reference_cpu_gemm<half_t,half_t,half_t,float>, the reference template's instantiation."""
+    g = np.load(path)
+    assert np.array_equal(oracle.cpu_gemm_f16(g["a"], g["b"], float(g["alpha"]), float(g["beta"])), g["c"])
+
+
+@pytest.mark.skipif(not oracle.have_reference(), reason="oracle/_ref not built (needs the reference checkout)")
+def test_fp16_oracle_matches_reference_build():
+    rng = np.random.Generator(np.random.Philox(5))
+    for (M, N, K) in ((1, 1, 1), (65, 33, 129), (128, 200, 555)):
+        a = oracle.f32_to_f16_bits(rng.standard_normal((M, K)).astype(np.float32))
+        b = oracle.f32_to_f16_bits((rng.standard_normal((N, K)) * 0.02).astype(np.float32))  # reaches subnormals
+        assert np.array_equal(oracle.cpu_gemm_f16(a, b), oracle.reference_cpu_gemm_f16(a, b))
+        assert np.array_equal(oracle.cpu_gemm_f16(a, b, 300.0, -2.0), oracle.reference_cpu_gemm_f16(a, b, 300.0, -2.0))
+
+
+def test_fp16_conversions_match_numpy():
+    lib = oracle._load_oracle()
+    import ctypes
+    lib.oracle_f32_to_f16.argtypes = [ctypes.c_float]
+    lib.oracle_f32_to_f16.restype = ctypes.c_uint16
+    lib.oracle_f16_to_f32.argtypes = [ctypes.c_uint16]
+    lib.oracle_f16_to_f32.restype = ctypes.c_float
+    rng = np.random.Generator(np.random.Philox(6))
+    x = np.concatenate([rng.standard_normal(3000).astype(np.float32) * s for s in (1e-8, 1e-5, 1e-3, 1, 100, 30000)]
+                       + [np.array([0, -0.0, 65504, 65519.99, 65520, 1e9, np.inf, 5.96e-8, 2.98e-8, 2.9e-8, 3.1e-8],
+                                   dtype=np.float32)])
+    with np.errstate(over="ignore"):
+        want = x.astype(np.float16).view(np.uint16)
+    got = np.array([lib.oracle_f32_to_f16(float(v)) for v in x], dtype=np.uint16)
+    assert np.array_equal(got, want)
+    for h in (0x0001, 0x03FF, 0x0400, 0x3C00, 0x7BFF, 0x7C00, 0x8001, 0xFBFF):
+        assert lib.oracle_f16_to_f32(h) == float(np.array([h], dtype=np.uint16).view(np.float16)[0])
 
 
 def test_oracle_matches_golden_config1():

@@ -27,6 +27,19 @@ def integer_bits(shape, seed: int) -> np.ndarray:
     return oracle.f32_to_bf16_bits(_rng(seed).integers(-5, 5, size=shape).astype(np.float32))
 
 
+def f16_uniform_bits(shape, seed: int) -> np.ndarray:
+    return oracle.f32_to_f16_bits(_rng(seed).uniform(-1.0, 1.0, size=shape).astype(np.float32))
+
+
+def f16_integer_bits(shape, seed: int) -> np.ndarray:
+    return oracle.f32_to_f16_bits(_rng(seed).integers(-5, 5, size=shape).astype(np.float32))
+
+
+def to_device_f16(bits: np.ndarray):
+    import torch
+    return torch.from_numpy(bits.view(np.int16)).cuda().view(torch.float16)
+
+
 def to_device(bits: np.ndarray):
     """numpy uint16 bit patterns -> torch bfloat16 CUDA tensor (same bits)."""
     import torch
