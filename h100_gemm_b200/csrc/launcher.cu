@@ -683,13 +683,17 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   lc.blockDim = dim3(static_cast<unsigned>(plan.kernel->threads), 1, 1);
   lc.dynamicSmemBytes = static_cast<size_t>(plan.smem);
   lc.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = plan.pair ? 2 : 1;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  lc.attrs = &attr;
-  lc.numAttrs = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = plan.pair ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  // Let this kernel's set-up overlap the tail of whatever runs before it in the stream; the
+  // kernel itself waits (griddepcontrol.wait) before it touches global memory.
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = std::getenv("B200_GEMM_NO_PDL") ? 0 : 1;
+  lc.attrs = attr;
+  lc.numAttrs = 2;
   // (the tracing build exists for bf16 only; fp16 launches are never traced)
   if (f16) args.profile = nullptr;
   const KernelFn fn = f16 ? plan.kernel->fn_f16 : (args.profile ? plan.kernel->fn_traced : plan.kernel->fn);

@@ -239,6 +239,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   volatile uint32_t* abort_flag = tmem_ptr_slot + 1;
 
   // ---------------------------------------------------------------- set-up
+  ptx::grid_launch_dependents();  // the next kernel in the stream may begin its own set-up
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
@@ -266,6 +267,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   }
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_slot;
+  // Programmatic dependent launch: everything above (barriers, tensor memory, descriptor prefetch)
+  // may overlap the tail of the previous kernel in the stream; nothing below may, because it reads
+  // or writes global memory that kernel may still be using (operands, C, partial tiles, flags).
+  ptx::grid_dependency_wait();
 
   // ---------------------------------------------------------------- roles
   if (warp == 0) {

@@ -55,6 +55,13 @@ B200_DEVICE uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
   return r;
 }
 
+// Programmatic dependent launch (stream order relaxed by the launch attribute
+// cudaLaunchAttributeProgrammaticStreamSerialization): `wait` blocks until every kernel this
+// launch depends on has completed and its memory is visible; `launch_dependents` lets the next
+// kernel in the stream start being scheduled. Both are no-ops for a launch without the attribute.
+B200_DEVICE void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+B200_DEVICE void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 B200_DEVICE void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }

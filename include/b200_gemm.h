@@ -81,7 +81,10 @@ typedef struct b200_gemm_cfg {
  * the reference's own GEMMs define (reference.h:40,72); alpha = 1, beta = 0 is the fast path the
  * reference's kernels hard-wire (matmul_h100.cu.jinja:696).
  * `workspace` may be NULL when b200_gemm_workspace_bytes() returns 0 for the same arguments.
- * Asynchronous on `stream`; no host synchronisation, no allocation. */
+ * Asynchronous on `stream`; no host synchronisation, no allocation. The kernel is launched with
+ * programmatic stream serialization: its set-up may overlap the tail of the kernel before it in
+ * the stream, and it waits for that kernel to complete before it reads or writes global memory
+ * (environment variable B200_GEMM_NO_PDL=1 turns this off). */
 int b200_gemm_bf16(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
                    float beta, const b200_gemm_cfg* cfg, void* workspace, size_t workspace_bytes,
                    void* stream);
