@@ -150,6 +150,14 @@ def cpu_sample(N, K, kind_a, kind_b, rows, cols):
     return draw((rows, K), kind_a), draw((min(cols, N), K), kind_b)
 
 
+def host_threads() -> int:
+    """All host cores, whatever OMP_NUM_THREADS a launcher exported (torchrun sets it to 1)."""
+    n = int(os.environ.get("B200_BENCH_THREADS", "0")) or (os.cpu_count() or 1)
+    from oracle import oracle
+    oracle.set_threads(n)
+    return n
+
+
 def cpu_gemm_fn():
     from oracle import oracle
     if oracle.have_reference():
@@ -169,8 +177,7 @@ def time_cpu(fn, a, b, repeats=1):
 
 def cpu_baseline(workload, hbm_bound):
     M, N, K, ka, kb = WORKLOADS[workload]
-    cores = os.cpu_count() or 1
-    threads = int(os.environ.get("OMP_NUM_THREADS", cores))
+    threads = host_threads()
     # The reference parallelises over 64-row blocks only (reference.h:14), so give every thread
     # one block; cap the columns so the sample stays within tens of seconds.
     rows = min(M, 64 * threads)
@@ -192,11 +199,11 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    workload = args.workload or "square8192"
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    workload = args.workload or ("square8192" if world == 1 else "prefill_shard")  # as our own arm
     M, N, K, ka, kb = WORKLOADS[workload]
     hbm = workload in HBM_BOUND
-    cores = os.cpu_count() or 1
-    threads = int(os.environ.get("OMP_NUM_THREADS", cores))
+    threads = host_threads()
     rows = min(M, 64 * threads)
     cols = N if hbm else min(N, 1024)
     a, b = cpu_sample(N, K, ka, kb, rows, cols)
@@ -341,7 +348,7 @@ def run_ours(args):
         dist.all_reduce(tg, op=dist.ReduceOp.MAX)
         g_ms = float(tg.item()) / args.steps
         gathered = {"value": world * 2.0 * M * N * K / (g_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": g_ms,
-                    "collective": "NCCL all_gather of C, 4 row chunks per shard overlapped with the next chunk's GEMM",
+                    "collective": "NCCL all-gather of C as grouped send/recv straight into place, 4 row chunks per shard overlapped with the next chunk's GEMM",
                     "bytes_received_per_gpu": int((world - 1) * M * N * 2)}
         del full
 

@@ -70,6 +70,9 @@ class ShardedGemm:
             raise ValueError("M must divide evenly over the ranks for the gathered layout")
         self.rows = M // self.world
 
+    def _global(self, group_rank: int) -> int:
+        return group_rank if self.group is None else self.dist.get_global_rank(self.group, group_rank)
+
     def compute(self, out_shard) -> None:
         """No collective: every rank fills its own rows."""
         self.gemm_fn(self.a, self.b, out_shard)
@@ -86,15 +89,24 @@ class ShardedGemm:
         for (r0, r1) in pieces:
             mine = out_full[self.begin + r0:self.begin + r1]
             self.gemm_fn(self.a[r0:r1], self.b, mine)
-            outs = [out_full[p * rows + r0:p * rows + r1] for p in range(self.world)]
             if self.world == 1:
                 continue
+            # Every peer's piece of this chunk is a contiguous row range of the full C, so the
+            # exchange is point-to-point sends and receives straight into place (one grouped NCCL
+            # launch, no staging copy), issued on the side stream while the next chunk multiplies.
+            ops = []
+            for step in range(1, self.world):
+                to = (self.rank + step) % self.world
+                frm = (self.rank - step) % self.world
+                ops.append(self.dist.P2POp(self.dist.isend, mine, self._global(to), group=self.group))
+                ops.append(self.dist.P2POp(self.dist.irecv, out_full[frm * rows + r0:frm * rows + r1],
+                                           self._global(frm), group=self.group))
             if use_cuda and comm_stream is not None:
                 comm_stream.wait_stream(main)
                 with torch.cuda.stream(comm_stream):
-                    handles.append(self.dist.all_gather(outs, mine, group=self.group, async_op=True))
+                    handles.extend(self.dist.batch_isend_irecv(ops))
             else:
-                self.dist.all_gather(outs, mine, group=self.group)
+                handles.extend(self.dist.batch_isend_irecv(ops))
         for h in handles:
             h.wait()
         if use_cuda and comm_stream is not None:

@@ -27,6 +27,18 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* Number of OpenMP threads later calls use (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
 
 static inline float bf16_to_f32(uint16_t h) {
   uint32_t u = (uint32_t)h << 16;

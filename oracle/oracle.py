@@ -62,6 +62,18 @@ def _load_ref() -> ctypes.CDLL:
     return _ref
 
 
+def set_threads(n: int) -> None:
+    """OpenMP threads for the oracle and, when built, the reference library."""
+    lib = _load_oracle()
+    lib.oracle_set_threads.argtypes = [ctypes.c_int]
+    lib.oracle_set_threads(int(n))
+    if have_reference():
+        ref = _load_ref()
+        if hasattr(ref, "ref_set_threads"):
+            ref.ref_set_threads.argtypes = [ctypes.c_int]
+            ref.ref_set_threads(int(n))
+
+
 def _check(a: np.ndarray, b: np.ndarray):
     assert a.dtype == np.uint16 and b.dtype == np.uint16
     assert a.ndim == 2 and b.ndim == 2 and a.shape[1] == b.shape[1]

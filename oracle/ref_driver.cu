@@ -10,8 +10,15 @@
 // Used to (1) pin oracle/cpu_gemm.c bit for bit, (2) generate tests/golden/, and (3) time the
 // reference's own CPU GEMM as the benchmark's reference arm.
 #include <cuda_bf16.h>
+#include <omp.h>
 
 #include "reference.h"
+
+// Number of OpenMP threads reference_cpu_gemm's `omp parallel for` uses from now on (launchers
+// such as torchrun export OMP_NUM_THREADS=1).
+extern "C" void ref_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+}
 
 extern "C" void ref_cpu_gemm_f16(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
                                  float beta) {
