@@ -273,7 +273,7 @@ def run_ours(args):
         rot = 3
         bs = [b] + [b.clone() for _ in range(rot - 1)]
     stream = torch.cuda.current_stream()
-    launches_per_step = 1 + (1 if cfg.sched != 0 else 0)
+    launches_per_step = 1 + (1 if cfg.sched == 1 else 0)  # split-K alone adds a fix-up kernel
 
     def step(i):
         g.gemm(a, bs[i % rot], out=c, cfg=cfg, workspace=ws, stream=stream)
