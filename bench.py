@@ -41,9 +41,9 @@ WORKLOADS = {
 HBM_BOUND = {"skinny16", "skinny32", "skinny64", "skinny128"}
 
 # DRAM bytes (read + write) of one gemm_kernel launch, from the ncu captures summarised in
-# profiles/gemm_kernel_square8192.md (822.9 MB read + 120.4 MB written) and
-# profiles/gemm_kernel_skinny16.md (471.3 MB + 5.05 MB); None where no capture exists.
-NCU_DRAM_BYTES_PER_LAUNCH = {"square8192": 9.433e8, "prefill_shard": 9.433e8, "skinny16": 4.763e8}
+# profiles/gemm_kernel_square8192.md (821.4 MB read + 120.2 MB written) and
+# profiles/gemm_kernel_skinny16.md (471.3 MB + 4.9 MB); None where no capture exists.
+NCU_DRAM_BYTES_PER_LAUNCH = {"square8192": 9.416e8, "prefill_shard": 9.416e8, "skinny16": 4.762e8}
 
 
 def measured_peaks():
