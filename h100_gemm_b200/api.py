@@ -106,6 +106,17 @@ def library() -> ctypes.CDLL:
     if hasattr(lib, "b200_gemm_bf16_fixed_scratch"):
         lib.b200_gemm_bf16_fixed_scratch.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf, vp]
         lib.b200_gemm_bf16_fixed_scratch.restype = ci
+    if hasattr(lib, "b200_gemm_bf16_gather"):
+        lib.b200_gemm_bf16_gather.argtypes = [ci, ci, ci, vp, vp, ctypes.POINTER(vp), ci, ci, cfgp, vp]
+        lib.b200_gemm_bf16_gather.restype = ci
+        lib.b200_peer_alloc.argtypes = [sz, ctypes.POINTER(vp)]
+        lib.b200_peer_free.argtypes = [vp]
+        lib.b200_peer_export.argtypes = [vp, ctypes.c_char_p]
+        lib.b200_peer_import.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+        lib.b200_peer_close.argtypes = [vp]
+        for f in (lib.b200_peer_alloc, lib.b200_peer_free, lib.b200_peer_export, lib.b200_peer_import,
+                  lib.b200_peer_close):
+            f.restype = ci
     lib.b200_gemm_strerror.argtypes = [ci]
     lib.b200_gemm_strerror.restype = ctypes.c_char_p
     lib.b200_gemm_last_cuda_error.argtypes = []
@@ -218,6 +229,68 @@ def gemm_fixed_scratch(a, b, out=None, alpha: float = 1.0, beta: float = 0.0, st
     _check(library().b200_gemm_bf16_fixed_scratch(M, N, K, a.data_ptr(), b.data_ptr(), out.data_ptr(), alpha,
                                                   beta, _stream_ptr(stream)))
     return out
+
+
+class DeviceBuffer:
+    """A cudaMalloc allocation other processes of the node can map (CUDA IPC), viewable as a torch
+    tensor. Used for the per-rank copies of C that the fused gather GEMM writes into."""
+
+    def __init__(self, nbytes: int):
+        self.nbytes = nbytes
+        p = ctypes.c_void_p()
+        _check(library().b200_peer_alloc(nbytes, ctypes.byref(p)))
+        self.ptr = p.value
+        self._imported = False
+
+    @classmethod
+    def from_handle(cls, handle: bytes, nbytes: int) -> "DeviceBuffer":
+        self = cls.__new__(cls)
+        p = ctypes.c_void_p()
+        _check(library().b200_peer_import(handle, ctypes.byref(p)))
+        self.ptr, self.nbytes, self._imported = p.value, nbytes, True
+        return self
+
+    def handle(self) -> bytes:
+        buf = ctypes.create_string_buffer(64)
+        _check(library().b200_peer_export(self.ptr, buf))
+        return buf.raw
+
+    def tensor(self, shape, dtype=None):
+        """A torch view of the allocation (no copy)."""
+        import torch
+        dtype = dtype or torch.bfloat16
+        n = 1
+        for d in shape:
+            n *= d
+
+        class _Raw:
+            pass
+
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (n,), "typestr": "<i2", "data": (self.ptr, False), "version": 2}
+        return torch.as_tensor(raw, device="cuda").view(dtype).view(*shape)
+
+    def close(self) -> None:
+        if self.ptr:
+            if self._imported:
+                library().b200_peer_close(self.ptr)
+            else:
+                library().b200_peer_free(self.ptr)
+            self.ptr = None
+
+
+def gemm_gather(a, b, c_all_ptrs, rank: int, cfg: Optional[GemmConfig] = None, stream=None) -> None:
+    """Fused GEMM + all-gather (b200_gemm_bf16_gather): writes this rank's rows of C = a @ b^T into
+    every pointer of `c_all_ptrs` (one full-C buffer per rank). The caller orders completion."""
+    _require_cuda_bf16(a, "a", 2)
+    _require_cuda_bf16(b, "b", 2)
+    M, K = a.shape
+    N = b.shape[0]
+    world = len(c_all_ptrs)
+    arr = (ctypes.c_void_p * world)(*c_all_ptrs)
+    keep, p = _cfg_ptr(cfg)
+    _check(library().b200_gemm_bf16_gather(M, N, K, a.data_ptr(), b.data_ptr(), arr, world, rank, p,
+                                           _stream_ptr(stream)))
 
 
 def gemm_batched(a, b, out=None, alpha: float = 1.0, beta: float = 0.0,

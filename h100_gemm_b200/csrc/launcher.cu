@@ -146,7 +146,8 @@ __global__ void naive_gemm_kernel(int M, int N, int K, const T* __restrict__ A, 
 // ------------------------------------------------------------------------------------------
 // Kernel table
 // ------------------------------------------------------------------------------------------
-using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmArgs);
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const StoreMaps<1>, const GemmArgs);
+using GatherFn = void (*)(const CUtensorMap, const CUtensorMap, const StoreMaps<kMaxGatherPeers>, const GemmArgs);
 
 struct KernelEntry {
   int bn;
@@ -155,6 +156,7 @@ struct KernelEntry {
   KernelFn fn;
   KernelFn fn_traced;  // same kernel with the cycle counters compiled in
   KernelFn fn_f16;     // same kernel for IEEE fp16 operands and output
+  GatherFn fn_gather;  // same kernel storing every tile to up to 8 copies of C (256-column pair tiles only)
   int b_bytes;    // bytes of B staged per CTA and K-tile
   int b_rows_cta;
   int block_m;    // rows of C per worker tile
@@ -163,14 +165,24 @@ struct KernelEntry {
 };
 
 template <int BN, int PAIR, int MT>
+GatherFn gather_variant() {
+  if constexpr (BN == 256 && PAIR == 1) {
+    return &gemm_kernel<BN, PAIR, MT, 0, 0, kMaxGatherPeers>;
+  } else {
+    return nullptr;
+  }
+}
+
+template <int BN, int PAIR, int MT>
 KernelEntry make_entry() {
   using T = KernelTraits<BN, PAIR, MT>;
   return KernelEntry{BN,
                      PAIR,
                      MT,
-                     &gemm_kernel<BN, PAIR, MT, 0, 0>,
-                     &gemm_kernel<BN, PAIR, MT, 1, 0>,
-                     &gemm_kernel<BN, PAIR, MT, 0, 1>,
+                     &gemm_kernel<BN, PAIR, MT, 0, 0, 1>,
+                     &gemm_kernel<BN, PAIR, MT, 1, 0, 1>,
+                     &gemm_kernel<BN, PAIR, MT, 0, 1, 1>,
+                     gather_variant<BN, PAIR, MT>(),
                      T::kBBytes,
                      T::kBRowsCta,
                      T::kBlockM,
@@ -251,6 +263,9 @@ int max_resident_workers(DeviceState& st, const KernelEntry& e, int smem, int* o
   B200_CUDA_TRY(cudaFuncSetAttribute(e.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
   B200_CUDA_TRY(cudaFuncSetAttribute(e.fn_traced, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
   B200_CUDA_TRY(cudaFuncSetAttribute(e.fn_f16, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+  if (e.fn_gather != nullptr) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(e.fn_gather, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+  }
   if (smem > st.smem_optin) return B200_ERR_SMEM;
   int workers = st.sm_count;
   if (e.pair) {
@@ -555,7 +570,7 @@ int validate(int batch, int M, int N, int K, const void* A, const void* B, const
 int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, const void* B,
              long long strideB, void* C, long long strideC, float alpha, float beta,
              const b200_gemm_cfg* user_cfg, void* workspace, size_t workspace_bytes,
-             cudaStream_t stream, int f16 = 0) {
+             cudaStream_t stream, int f16 = 0, void* const* gather_dst = nullptr, int gather_world = 0) {
   int rc = validate(batch, M, N, K, A, B, C);
   if (rc != B200_OK) return rc;
   b200_gemm_cfg cfg = user_cfg ? *user_cfg : default_cfg(batch, M, N, K);
@@ -636,6 +651,7 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   const bool c_tma = store_mode == kStoreTma;
 
   CUtensorMap map_a, map_b, map_c;
+  StoreMaps<kMaxGatherPeers> gather_maps;
   rc = make_tensor_map(&map_a, a_src, pr.K, pr.M, pr.batch, a_pitch * 2, a_bstride * 2, kBlockK, a_rows);
   if (rc != B200_OK) return rc;
   rc = make_tensor_map(&map_b, b_src, pr.K, pr.N, pr.batch, b_pitch * 2, b_bstride * 2, kBlockK,
@@ -647,6 +663,20 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
     if (rc != B200_OK) return rc;
   } else {
     map_c = map_a;  // never dereferenced by the store path
+  }
+  if (gather_world > 0) {
+    // Fused all-gather: needs the TMA-store epilogue, whole data-parallel tiles and the kernel
+    // variant that takes one map per destination.
+    if (!c_tma || plan.kernel->fn_gather == nullptr || args.sched.mode != kDataParallel || f16 ||
+        gather_world > kMaxGatherPeers || pr.batch != 1) {
+      return B200_ERR_UNSUPPORTED_CFG;
+    }
+    for (int p = 0; p < kMaxGatherPeers; ++p) {
+      const int src = p < gather_world ? p : 0;
+      rc = make_tensor_map(&gather_maps.m[p], gather_dst[src], pr.N, pr.M, 1, static_cast<uint64_t>(pr.N) * 2, 0,
+                           kEpiChunkCols, 32);
+      if (rc != B200_OK) return rc;
+    }
   }
 
   args.M = pr.M;
@@ -694,10 +724,17 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   attr[1].val.programmaticStreamSerializationAllowed = std::getenv("B200_GEMM_NO_PDL") ? 0 : 1;
   lc.attrs = attr;
   lc.numAttrs = 2;
-  // (the tracing build exists for bf16 only; fp16 launches are never traced)
-  if (f16) args.profile = nullptr;
-  const KernelFn fn = f16 ? plan.kernel->fn_f16 : (args.profile ? plan.kernel->fn_traced : plan.kernel->fn);
-  B200_CUDA_TRY(cudaLaunchKernelEx(&lc, fn, map_a, map_b, map_c, args));
+  // (the tracing build exists for bf16 only; fp16 and fused-gather launches are never traced)
+  if (f16 || gather_world > 0) args.profile = nullptr;
+  args.gather_world = gather_world;
+  if (gather_world > 0) {
+    B200_CUDA_TRY(cudaLaunchKernelEx(&lc, plan.kernel->fn_gather, map_a, map_b, gather_maps, args));
+  } else {
+    const KernelFn fn = f16 ? plan.kernel->fn_f16 : (args.profile ? plan.kernel->fn_traced : plan.kernel->fn);
+    StoreMaps<1> one;
+    one.m[0] = map_c;
+    B200_CUDA_TRY(cudaLaunchKernelEx(&lc, fn, map_a, map_b, one, args));
+  }
 
   if (args.sched.mode == kSplitK && sched_num_slots(args.sched) > 0) {
     const int block_m = plan.kernel->block_m;
@@ -860,6 +897,70 @@ int b200_gemm_bf16_fixed_scratch(int M, int N, int K, const void* A, const void*
   rc = run_gemm(1, M, N, K, A, 0, B, 0, C, 0, alpha, beta, &cfg, scratch, kStaticScratchBytes,
                 static_cast<cudaStream_t>(stream));
   return rc == B200_ERR_WORKSPACE ? B200_ERR_STATIC_SCRATCH : rc;
+}
+
+// ------------------------------------------------------------------------------------------
+// Row-sharded GEMM fused with the all-gather of C
+// ------------------------------------------------------------------------------------------
+int b200_gemm_bf16_gather(int M, int N, int K, const void* A, const void* B, void* const* C_all, int world,
+                          int rank, const b200_gemm_cfg* cfg, void* stream) {
+  if (C_all == nullptr || world < 1 || world > kMaxGatherPeers || rank < 0 || rank >= world) {
+    return B200_ERR_INVALID_ARG;
+  }
+  if (M <= 0 || N <= 0 || K <= 0 || N % 8 != 0) return B200_ERR_INVALID_ARG;
+  // Destination p is rank p's copy of the full [world * M, N] matrix; this rank's rows start at
+  // rank * M in every copy.
+  void* dst[kMaxGatherPeers] = {};
+  for (int p = 0; p < world; ++p) {
+    if (C_all[p] == nullptr) return B200_ERR_INVALID_ARG;
+    dst[p] = static_cast<__nv_bfloat16*>(C_all[p]) + static_cast<size_t>(rank) * M * N;
+  }
+  b200_gemm_cfg c = cfg ? *cfg : default_cfg(1, M, N, K);
+  if (cfg == nullptr) {
+    // the fused epilogue exists for 256-column pair tiles with TMA stores
+    c.cluster_m = 2;
+    c.block_n = 256;
+    if (c.block_m != 256) c.block_m = 128;
+    c.sched = kDataParallel;
+    c.epilogue = 1;
+  }
+  return run_gemm(1, M, N, K, A, 0, B, 0, dst[rank], 0, 1.0f, 0.0f, &c, nullptr, 0, static_cast<cudaStream_t>(stream),
+                  /*f16=*/0, dst, world);
+}
+
+// Peer-visible device memory for the call above: plain cudaMalloc allocations whose CUDA IPC
+// handles the ranks of one node exchange (over any channel that moves 64 bytes).
+int b200_peer_alloc(size_t bytes, void** ptr) {
+  if (ptr == nullptr || bytes == 0) return B200_ERR_INVALID_ARG;
+  B200_CUDA_TRY(cudaMalloc(ptr, bytes));
+  return B200_OK;
+}
+
+int b200_peer_free(void* ptr) {
+  B200_CUDA_TRY(cudaFree(ptr));
+  return B200_OK;
+}
+
+int b200_peer_export(void* ptr, unsigned char handle[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handles are 64 bytes");
+  if (ptr == nullptr || handle == nullptr) return B200_ERR_INVALID_ARG;
+  cudaIpcMemHandle_t h;
+  B200_CUDA_TRY(cudaIpcGetMemHandle(&h, ptr));
+  std::memcpy(handle, &h, sizeof(h));
+  return B200_OK;
+}
+
+int b200_peer_import(const unsigned char handle[64], void** ptr) {
+  if (ptr == nullptr || handle == nullptr) return B200_ERR_INVALID_ARG;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, sizeof(h));
+  B200_CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return B200_OK;
+}
+
+int b200_peer_close(void* ptr) {
+  B200_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return B200_OK;
 }
 
 int b200_reference_gpu_gemm_bf16(int M, int N, int K, const void* A, const void* B, void* C,

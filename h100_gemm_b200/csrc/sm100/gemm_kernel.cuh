@@ -84,6 +84,7 @@ struct GemmArgs {
   int M, N, K, batch;
   SchedParams sched;
   int stages;
+  int gather_world;           // fused all-gather: number of destination copies of C (0 = plain GEMM)
   int f16;                    // 0: bf16 inputs and output; 1: IEEE fp16 (selects the F16 kernel; used by fix-up)
   int store_mode;             // StoreMode: how the epilogue writes C
   int epi_bytes;              // shared memory reserved for TMA-store staging (0 unless kStoreTma)
@@ -197,10 +198,19 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
   return r;
 }
 
-template <int BN, int PAIR, int MT, int PROF, int F16>
+// Tensor maps the epilogue stores C through: one for an ordinary GEMM; one per destination when
+// the kernel also performs the all-gather of a row-sharded C (every rank's copy of the full C,
+// this rank's own included, reached through peer-mapped device memory over NVLink).
+static constexpr int kMaxGatherPeers = 8;
+template <int NP>
+struct StoreMaps {
+  CUtensorMap m[NP];
+};
+
+template <int BN, int PAIR, int MT, int PROF, int F16, int NP>
 __global__ void __launch_bounds__((KernelTraits<BN, PAIR, MT>::kThreads), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-            const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmArgs args) {
+            const __grid_constant__ StoreMaps<NP> maps_c, const __grid_constant__ GemmArgs args) {
   using T = KernelTraits<BN, PAIR, MT>;
   constexpr int G = T::kCtaGroup;
   constexpr int kAccStages = T::kAccStages;
@@ -243,7 +253,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
-    ptx::prefetch_tensormap(&map_c);
+    for (int p = 0; p < (NP > 1 ? args.gather_world : 1); ++p) ptx::prefetch_tensormap(&maps_c.m[p]);
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(full_bar(s), 1);
       ptx::mbar_init(empty_bar(s), 1);
@@ -634,7 +644,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          ptx::tma_store_3d(&map_c, slab, n0, m_slab, tc.b);
+          if constexpr (NP > 1) {
+            // fused all-gather: the same staged block goes to every rank's copy of C (one bulk
+            // group, so the slab is reused only after all of them have read it)
+            for (int p = 0; p < args.gather_world; ++p) ptx::tma_store_3d(&maps_c.m[p], slab, n0, m_slab, tc.b);
+          } else {
+            ptx::tma_store_3d(&maps_c.m[0], slab, n0, m_slab, tc.b);
+          }
           ptx::tma_store_commit();
         }
         ++store_count;

@@ -111,3 +111,48 @@ class ShardedGemm:
             h.wait()
         if use_cuda and comm_stream is not None:
             main.wait_stream(comm_stream)
+
+
+class FusedGatherGemm:
+    """C = A @ B^T with A row-sharded over the ranks of one node and the all-gather of C done by
+    the GEMM kernel itself: every rank owns a full-C buffer that the other ranks map through CUDA
+    IPC, and each rank's epilogue stores its tiles into all of them over NVLink (TMA stores to
+    peer memory; no multicast, no library collective on the data path).
+
+    Completion is ordered by a one-element all-reduce on the launching stream: it finishes on a
+    rank only after every rank has enqueued it behind its own GEMM launch.
+    """
+
+    def __init__(self, M_shard: int, N: int, group=None):
+        import torch
+        import torch.distributed as dist
+        from . import api
+        self.api, self.dist, self.group, self.torch = api, dist, group, torch
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("the fused gather covers the ranks of one node (at most 8)")
+        self.M, self.N = M_shard, N
+        nbytes = self.world * M_shard * N * 2
+        self.mine = api.DeviceBuffer(nbytes)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.mine.handle(), group=group)
+        self.peers = [self.mine if p == self.rank else api.DeviceBuffer.from_handle(handles[p], nbytes)
+                      for p in range(self.world)]
+        self.ptrs = [b.ptr for b in self.peers]
+        self.full = self.mine.tensor((self.world * M_shard, N))
+        self._token = torch.zeros(1, device="cuda")
+
+    def run(self, a_shard, b, cfg=None, stream=None) -> None:
+        """Enqueue the fused kernel and the completion barrier on the current stream."""
+        self.api.gemm_gather(a_shard, b, self.ptrs, self.rank, cfg=cfg, stream=stream)
+        self.dist.all_reduce(self._token, group=self.group)
+
+    def close(self) -> None:
+        self.torch.cuda.synchronize()
+        self.dist.barrier(group=self.group)
+        for p, buf in enumerate(self.peers):
+            if p != self.rank:
+                buf.close()
+        self.dist.barrier(group=self.group)
+        self.mine.close()

@@ -142,6 +142,28 @@ void b200_gemm_host_release(void);
 int b200_gemm_bf16_fixed_scratch(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
                                  float beta, void* stream);
 
+/* Row-sharded GEMM fused with the all-gather of C. Rank `rank` of `world` (<= 8) ranks on one node
+ * holds M rows of A; C_all[p] is the base of rank p's copy of the FULL C ([world * M, N], bf16,
+ * row-major) as addressable from this device — its own allocation for p == rank, peer-mapped
+ * memory (b200_peer_import) for the others. The kernel's epilogue writes every finished tile into
+ * all `world` copies with TMA stores over NVLink, so when every rank's launch has completed each
+ * rank holds the whole C; no separate collective runs. The caller must order "all launches
+ * complete" before anyone reads C (a barrier between the ranks, e.g. a one-element all-reduce on
+ * the same stream). Needs N % 8 == 0 and 16-byte aligned copies. cfg == NULL picks the pair-tile
+ * configuration the fused epilogue is built for; other tile shapes return
+ * B200_ERR_UNSUPPORTED_CFG. The reference has no multi-GPU path; this is the M-sharded
+ * configuration with the collective that follows the kernel folded into it. */
+int b200_gemm_bf16_gather(int M, int N, int K, const void* A, const void* B, void* const* C_all, int world,
+                          int rank, const b200_gemm_cfg* cfg, void* stream);
+
+/* Device memory that other processes on the node can map (CUDA IPC): allocate, export a 64-byte
+ * handle, import a peer's handle (enables peer access lazily), close an imported mapping, free. */
+int b200_peer_alloc(size_t bytes, void** ptr);
+int b200_peer_free(void* ptr);
+int b200_peer_export(void* ptr, unsigned char handle[64]);
+int b200_peer_import(const unsigned char handle[64], void** ptr);
+int b200_peer_close(void* ptr);
+
 /* Replaces reference_gpu_gemm(GemmParams) — reference.h:49-90: a plain SIMT GEMM (one thread per
  * 4x4 outputs, k ascending, fp32) used as an on-device cross-check for shapes too large for the
  * CPU oracle. */

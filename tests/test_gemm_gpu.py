@@ -240,6 +240,39 @@ def test_row_shards_concatenate_bit_exact(g):
     assert g.device_status()[0] == 0
 
 
+def test_fused_gather_epilogue_on_one_device(g):
+    """b200_gemm_bf16_gather with every "rank's" copy of C on this device: each call must fill
+    exactly its own row range in ALL copies, bit-identical to the plain GEMM, and leave the rest."""
+    import torch
+    from h100_gemm_b200 import api
+    world, M, N, K = 3, 1024, 768, 512
+    gen = torch.Generator(device="cuda").manual_seed(12)
+    b = (torch.randn(N, K, device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
+    shards = [torch.randn(M, K, device="cuda", generator=gen).to(torch.bfloat16) for _ in range(world)]
+    bufs = [api.DeviceBuffer(world * M * N * 2) for _ in range(world)]
+    try:
+        views = [buf.tensor((world * M, N)) for buf in bufs]
+        for v in views:
+            v.fill_(-7.0)
+        for cfg in (None, api.GemmConfig(block_m=128, block_n=256, cluster_m=2, epilogue=1)):
+            for rank in range(world):
+                api.gemm_gather(shards[rank], b, [buf.ptr for buf in bufs], rank, cfg=cfg)
+                assert g.device_status()[0] == 0
+                want = g.gemm(shards[rank], b)
+                for v in views:
+                    assert torch.equal(v[rank * M:(rank + 1) * M].view(torch.int16), want.view(torch.int16))
+                    later = v[(rank + 1) * M:]
+                    if cfg is None and later.numel():
+                        assert bool((later == -7.0).all())  # rows of ranks that have not run yet
+        # a tile shape the fused epilogue is not built for is refused, not mis-executed
+        with pytest.raises(api.GemmError) as e:
+            api.gemm_gather(shards[0], b, [buf.ptr for buf in bufs], 0, cfg=api.GemmConfig(block_n=128, cluster_m=1))
+        assert e.value.status == api.STATUS_UNSUPPORTED_CFG
+    finally:
+        for buf in bufs:
+            buf.close()
+
+
 # ------------------------------------------------------------------------------------------------
 # Configuration 5: irregular shapes and the batched problem.
 # ------------------------------------------------------------------------------------------------
