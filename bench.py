@@ -355,18 +355,23 @@ def run_ours(args):
         try:
             from h100_gemm_b200.sharding import FusedGatherGemm
             fg = FusedGatherGemm(M, N)
-            for _ in range(max(3, args.warmup)):
-                fg.run(a, b, stream=stream)
-            barrier()
-            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            f0.record(stream)
-            for _ in range(args.steps):
-                fg.run(a, b, stream=stream)
-            f1.record(stream)
-            torch.cuda.synchronize()
-            tf = torch.tensor([f0.elapsed_time(f1)], dtype=torch.float64, device=device)
-            dist.all_reduce(tf, op=dist.ReduceOp.MAX)
-            f_ms = float(tf.item()) / args.steps
+            variants = {}
+            for vname, vcfg in (("256 rows per CTA, one accumulator buffer", None),
+                                ("128 rows per CTA, two accumulator buffers",
+                                 g.GemmConfig(block_m=128, block_n=256, cluster_m=2, epilogue=1))):
+                for _ in range(max(3, args.warmup)):
+                    fg.run(a, b, cfg=vcfg, stream=stream)
+                barrier()
+                f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                f0.record(stream)
+                for _ in range(args.steps):
+                    fg.run(a, b, cfg=vcfg, stream=stream)
+                f1.record(stream)
+                torch.cuda.synchronize()
+                tf = torch.tensor([f0.elapsed_time(f1)], dtype=torch.float64, device=device)
+                dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+                variants[vname] = float(tf.item()) / args.steps
+            f_ms = min(variants.values())
             ref_rows = g.gemm(a, b)
             ok = bool(torch.equal(fg.full[rank * M:(rank + 1) * M].view(torch.int16), ref_rows.view(torch.int16)))
             # every rank's copy must hold the same bits: compare per-shard checksums across ranks
@@ -375,7 +380,9 @@ def run_ours(args):
             dist.all_gather(all_sums, sums)
             same = all(bool(torch.equal(all_sums[0], s_)) for s_ in all_sums)
             gathered["fused"] = {"value": world * 2.0 * M * N * K / (f_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                                 "ms_per_step": f_ms, "own_rows_match": ok, "all_copies_identical": same,
+                                 "ms_per_step": f_ms, "ms_per_step_by_tile": variants, "own_rows_match": ok,
+                                 "all_copies_identical": same,
+                                 "nvlink_bytes_out_per_gpu": int((world - 1) * M * N * 2),
                                  "collective": "none: the GEMM epilogue stores every tile into all ranks' C over NVLink "
                                                "(TMA stores to peer-mapped memory), then a one-element all-reduce"}
             fg.close()
