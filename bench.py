@@ -359,8 +359,12 @@ def run_ours(args):
             for vname, vcfg in (("256 rows per CTA, one accumulator buffer", None),
                                 ("128 rows per CTA, two accumulator buffers",
                                  g.GemmConfig(block_m=128, block_n=256, cluster_m=2, epilogue=1))):
-                for _ in range(max(3, args.warmup)):
-                    fg.run(a, b, cfg=vcfg, stream=stream)
+                try:
+                    for _ in range(max(3, args.warmup)):
+                        fg.run(a, b, cfg=vcfg, stream=stream)
+                except RuntimeError as exc:      # same answer on every rank: a configuration the kernel lacks
+                    variants[vname] = None
+                    continue
                 barrier()
                 f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 f0.record(stream)
@@ -371,7 +375,7 @@ def run_ours(args):
                 tf = torch.tensor([f0.elapsed_time(f1)], dtype=torch.float64, device=device)
                 dist.all_reduce(tf, op=dist.ReduceOp.MAX)
                 variants[vname] = float(tf.item()) / args.steps
-            f_ms = min(variants.values())
+            f_ms = min(v for v in variants.values() if v is not None)
             ref_rows = g.gemm(a, b)
             ok = bool(torch.equal(fg.full[rank * M:(rank + 1) * M].view(torch.int16), ref_rows.view(torch.int16)))
             # every rank's copy must hold the same bits: compare per-shard checksums across ranks

@@ -910,10 +910,13 @@ int b200_gemm_bf16_gather(int M, int N, int K, const void* A, const void* B, voi
   if (M <= 0 || N <= 0 || K <= 0 || N % 8 != 0) return B200_ERR_INVALID_ARG;
   // Destination p is rank p's copy of the full [world * M, N] matrix; this rank's rows start at
   // rank * M in every copy.
+  // The kernel stores to its destinations in list order; the list starts with this rank's own copy
+  // and continues with rank+1, rank+2, ... so that at any moment the ranks aim at different peers.
   void* dst[kMaxGatherPeers] = {};
-  for (int p = 0; p < world; ++p) {
+  for (int i = 0; i < world; ++i) {
+    const int p = (rank + i) % world;
     if (C_all[p] == nullptr) return B200_ERR_INVALID_ARG;
-    dst[p] = static_cast<__nv_bfloat16*>(C_all[p]) + static_cast<size_t>(rank) * M * N;
+    dst[i] = static_cast<__nv_bfloat16*>(C_all[p]) + static_cast<size_t>(rank) * M * N;
   }
   b200_gemm_cfg c = cfg ? *cfg : default_cfg(1, M, N, K);
   if (cfg == nullptr) {
@@ -924,7 +927,7 @@ int b200_gemm_bf16_gather(int M, int N, int K, const void* A, const void* B, voi
     c.sched = kDataParallel;
     c.epilogue = 1;
   }
-  return run_gemm(1, M, N, K, A, 0, B, 0, dst[rank], 0, 1.0f, 0.0f, &c, nullptr, 0, static_cast<cudaStream_t>(stream),
+  return run_gemm(1, M, N, K, A, 0, B, 0, dst[0], 0, 1.0f, 0.0f, &c, nullptr, 0, static_cast<cudaStream_t>(stream),
                   /*f16=*/0, dst, world);
 }
 
