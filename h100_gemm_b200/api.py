@@ -117,6 +117,16 @@ def library() -> ctypes.CDLL:
         for f in (lib.b200_peer_alloc, lib.b200_peer_free, lib.b200_peer_export, lib.b200_peer_import,
                   lib.b200_peer_close):
             f.restype = ci
+    lib.b200_gemm_tuning_load.argtypes = [ctypes.c_char_p]
+    lib.b200_gemm_tuning_load.restype = ci
+    lib.b200_gemm_tuning_add.argtypes = [ci, ci, ci, ci, cfgp]
+    lib.b200_gemm_tuning_add.restype = ci
+    lib.b200_gemm_tuning_clear.argtypes = []
+    lib.b200_gemm_tuning_clear.restype = None
+    lib.b200_gemm_tuning_size.argtypes = []
+    lib.b200_gemm_tuning_size.restype = ci
+    lib.b200_gemm_heuristic_cfg.argtypes = [ci, ci, ci, ci, cfgp]
+    lib.b200_gemm_heuristic_cfg.restype = ci
     lib.b200_gemm_strerror.argtypes = [ci]
     lib.b200_gemm_strerror.restype = ctypes.c_char_p
     lib.b200_gemm_last_cuda_error.argtypes = []
@@ -168,6 +178,34 @@ def default_config(batch: int, M: int, N: int, K: int) -> GemmConfig:
     c = _Cfg()
     _check(library().b200_gemm_default_cfg(batch, M, N, K, ctypes.byref(c)))
     return GemmConfig(**{n: getattr(c, n) for n, _ in _Cfg._fields_})
+
+
+def heuristic_config(batch: int, M: int, N: int, K: int) -> GemmConfig:
+    """The built-in choice for a shape, ignoring the tuning table."""
+    c = _Cfg()
+    _check(library().b200_gemm_heuristic_cfg(batch, M, N, K, ctypes.byref(c)))
+    return GemmConfig(**{n: getattr(c, n) for n, _ in _Cfg._fields_})
+
+
+def tuning_load(path) -> int:
+    """Adds the entries of a tuning-table file (the format `gemm_tuner.py --table` writes) to the
+    table that ``cfg=None`` calls consult before the heuristic; returns how many were read."""
+    n = int(library().b200_gemm_tuning_load(str(path).encode()))
+    if n < 0:
+        raise GemmError(-n, f"tuning table {path}: {library().b200_gemm_strerror(-n).decode()}")
+    return n
+
+
+def tuning_add(M: int, N: int, K: int, cfg: GemmConfig, batch: int = 1) -> None:
+    _check(library().b200_gemm_tuning_add(batch, M, N, K, ctypes.byref(cfg._c())))
+
+
+def tuning_clear() -> None:
+    library().b200_gemm_tuning_clear()
+
+
+def tuning_size() -> int:
+    return int(library().b200_gemm_tuning_size())
 
 
 def _workspace(nbytes: int, workspace, device):

@@ -14,6 +14,8 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cmath>
+#include <cstdio>
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
@@ -355,7 +357,7 @@ struct Plan {
 // model: waves of tiles over the workers x tile area per SM x a penalty for the L2 -> shared
 // memory traffic each tile shape needs per FLOP (larger tiles move fewer bytes, which on a
 // power-limited part buys clock; smaller tiles fill the machine when there are few of them).
-b200_gemm_cfg default_cfg(int batch, int M, int N, int K) {
+b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K) {
   b200_gemm_cfg c;
   std::memset(&c, 0, sizeof(c));
   c.block_m = 128;
@@ -475,6 +477,146 @@ int fit_stages(Plan* p, int a_rows, int epi_bytes) {
   return B200_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// Tuning table: measured configurations per shape class, consulted before the heuristic
+// ------------------------------------------------------------------------------------------
+// The reference's tuner searches one shape and leaves the result to the reader (a JSON file and a
+// rendered best_matmul_h100.cu, gemm_tuner.py:126-145). Here the tuner's result is fed back: a
+// table of (batch, M, N, K) -> configuration that the cfg == NULL dispatch looks up first.
+// A shape's class is (batch > 1, ceil(log2 M), ceil(log2 N), ceil(log2 K)). A lookup takes the
+// exact shape if the table has it, otherwise the entry of the same class nearest in log2
+// distance, otherwise the built-in heuristic.
+struct TunedEntry {
+  int batch, M, N, K;
+  b200_gemm_cfg cfg;
+};
+std::vector<TunedEntry> g_tuned;
+std::mutex g_tuned_mutex;
+std::once_flag g_tuned_env_once;
+constexpr size_t kMaxTunedEntries = 4096;
+
+int log2_ceil(long long x) {
+  int b = 0;
+  while ((1LL << b) < x) ++b;
+  return b;
+}
+
+// An entry must name a kernel that exists; which shapes it is good for is the table's business.
+int tuning_validate(int batch, int M, int N, int K, const b200_gemm_cfg& cfg) {
+  if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARG;
+  if (cfg.c_col_major != 0 || cfg.max_ctas != 0) return B200_ERR_INVALID_ARG;  // per-call choices, not tunables
+  Plan plan;
+  return resolve_plan(cfg, &plan);
+}
+
+void tuning_add_locked(const TunedEntry& n) {
+  for (TunedEntry& e : g_tuned) {
+    if (e.batch == n.batch && e.M == n.M && e.N == n.N && e.K == n.K) {
+      e.cfg = n.cfg;
+      return;
+    }
+  }
+  g_tuned.push_back(n);
+}
+
+// Text format, one entry per line, '#' starts a comment:
+//   batch M N K block_m block_n cluster_m stages sched split_k raster group epilogue
+// Returns the number of entries added (>= 0), or -B200_ERR_* when the file cannot be opened, a
+// line is malformed or names a configuration without a kernel; then nothing is added.
+int tuning_load_file(const char* path) {
+  FILE* f = std::fopen(path, "r");
+  if (f == nullptr) return -B200_ERR_INVALID_ARG;
+  std::vector<TunedEntry> read;
+  char line[512];
+  int status = B200_OK;
+  while (status == B200_OK && std::fgets(line, sizeof line, f) != nullptr) {
+    char* hash = std::strchr(line, '#');
+    if (hash != nullptr) *hash = '\0';
+    int v[13];
+    char extra;
+    const int n = std::sscanf(line, "%d %d %d %d %d %d %d %d %d %d %d %d %d %c", &v[0], &v[1], &v[2], &v[3], &v[4],
+                              &v[5], &v[6], &v[7], &v[8], &v[9], &v[10], &v[11], &v[12], &extra);
+    if (n <= 0) continue;  // blank line or comment
+    if (n != 13) {
+      status = B200_ERR_INVALID_ARG;
+      break;
+    }
+    TunedEntry e;
+    std::memset(&e, 0, sizeof e);
+    e.batch = v[0];
+    e.M = v[1];
+    e.N = v[2];
+    e.K = v[3];
+    e.cfg.block_m = v[4];
+    e.cfg.block_n = v[5];
+    e.cfg.block_k = kBlockK;
+    e.cfg.cluster_m = v[6];
+    e.cfg.cluster_n = 1;
+    e.cfg.stages = v[7];
+    e.cfg.sched = v[8];
+    e.cfg.split_k = v[9];
+    e.cfg.raster = v[10];
+    e.cfg.group = v[11];
+    e.cfg.epilogue = v[12];
+    status = tuning_validate(e.batch, e.M, e.N, e.K, e.cfg);
+    if (status == B200_OK && read.size() >= kMaxTunedEntries) status = B200_ERR_INVALID_ARG;
+    if (status == B200_OK) read.push_back(e);
+  }
+  std::fclose(f);
+  if (status != B200_OK) return -status;
+  std::lock_guard<std::mutex> lock(g_tuned_mutex);
+  if (g_tuned.size() + read.size() > kMaxTunedEntries) return -B200_ERR_INVALID_ARG;
+  for (const TunedEntry& e : read) tuning_add_locked(e);
+  return static_cast<int>(read.size());
+}
+
+bool tuning_lookup(int batch, int M, int N, int K, b200_gemm_cfg* out) {
+  // B200_GEMM_TUNING_TABLE names a table file to load before the first lookup (errors: ignored
+  // here, the table simply stays empty; b200_gemm_tuning_load reports them).
+  std::call_once(g_tuned_env_once, [] {
+    const char* path = std::getenv("B200_GEMM_TUNING_TABLE");
+    if (path != nullptr && path[0] != '\0') (void)tuning_load_file(path);
+  });
+  std::lock_guard<std::mutex> lock(g_tuned_mutex);
+  if (g_tuned.empty()) return false;
+  const int cm = log2_ceil(M), cn = log2_ceil(N), ck = log2_ceil(K);
+  const TunedEntry* best = nullptr;
+  double best_d = 0.0;
+  for (const TunedEntry& e : g_tuned) {
+    if ((e.batch > 1) != (batch > 1)) continue;
+    if (e.batch == batch && e.M == M && e.N == N && e.K == K) {
+      *out = e.cfg;
+      return true;
+    }
+    if (log2_ceil(e.M) != cm || log2_ceil(e.N) != cn || log2_ceil(e.K) != ck) continue;
+    const double d = std::fabs(std::log2(static_cast<double>(e.M) / M)) +
+                     std::fabs(std::log2(static_cast<double>(e.N) / N)) +
+                     std::fabs(std::log2(static_cast<double>(e.K) / K));
+    if (best == nullptr || d < best_d) {
+      best = &e;
+      best_d = d;
+    }
+  }
+  if (best == nullptr) return false;
+  *out = best->cfg;
+  return true;
+}
+
+// What cfg == NULL means: the tuning table's answer for the shape's class, else the heuristic.
+b200_gemm_cfg default_cfg(int batch, int M, int N, int K) {
+  b200_gemm_cfg c;
+  if (tuning_lookup(batch, M, N, K, &c)) {
+    // An entry tuned on a neighbouring shape may ask for more stages than this shape's A tile
+    // leaves room for: then take as many as fit.
+    Plan plan;
+    if (resolve_plan(c, &plan) == B200_OK) {
+      if (fit_stages(&plan, a_rows_for(plan, M), epi_bytes_for(plan, plan.store_mode)) != B200_OK) c.stages = 0;
+      return c;
+    }
+  }
+  return heuristic_cfg(batch, M, N, K);
+}
+
 struct Problem {
   int batch, M, N, K;          // as the kernel sees them (after a column-major swap)
   const void* A;
@@ -574,9 +716,6 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   int rc = validate(batch, M, N, K, A, B, C);
   if (rc != B200_OK) return rc;
   b200_gemm_cfg cfg = user_cfg ? *user_cfg : default_cfg(batch, M, N, K);
-  if (user_cfg == nullptr && M <= 128 && N > 128) {
-    // nothing: default_cfg already chose the few-rows plan
-  }
   Plan plan;
   rc = resolve_plan(cfg, &plan);
   if (rc != B200_OK) return rc;
@@ -837,6 +976,40 @@ int b200_gemm_default_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg) {
   return B200_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// Tuning table (C ABI)
+// ------------------------------------------------------------------------------------------
+int b200_gemm_tuning_load(const char* path) {
+  if (path == nullptr) return -B200_ERR_INVALID_ARG;
+  return tuning_load_file(path);
+}
+
+int b200_gemm_tuning_add(int batch, int M, int N, int K, const b200_gemm_cfg* cfg) {
+  if (cfg == nullptr) return B200_ERR_INVALID_ARG;
+  const int rc = tuning_validate(batch, M, N, K, *cfg);
+  if (rc != B200_OK) return rc;
+  std::lock_guard<std::mutex> lock(g_tuned_mutex);
+  if (g_tuned.size() >= kMaxTunedEntries) return B200_ERR_INVALID_ARG;
+  tuning_add_locked(TunedEntry{batch, M, N, K, *cfg});
+  return B200_OK;
+}
+
+void b200_gemm_tuning_clear(void) {
+  std::lock_guard<std::mutex> lock(g_tuned_mutex);
+  g_tuned.clear();
+}
+
+int b200_gemm_tuning_size(void) {
+  std::lock_guard<std::mutex> lock(g_tuned_mutex);
+  return static_cast<int>(g_tuned.size());
+}
+
+int b200_gemm_heuristic_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg) {
+  if (cfg == nullptr || batch <= 0 || M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARG;
+  *cfg = heuristic_cfg(batch, M, N, K);
+  return B200_OK;
+}
+
 int b200_run_kernel(int M, int N, int K, void* A, void* B, void* C, int* DB) {
   (void)DB;
   if (M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARG;
@@ -875,7 +1048,7 @@ int b200_gemm_bf16_fixed_scratch(int M, int N, int K, const void* A, const void*
   if (M > kCtaRows || K % 8 != 0 || (reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(B) & 15u)) {
     return B200_ERR_STATIC_SCRATCH;
   }
-  b200_gemm_cfg cfg = default_cfg(1, M, N, K);
+  b200_gemm_cfg cfg = heuristic_cfg(1, M, N, K);  // never the tuning table: the scratch is sized for this plan
   if (b200_gemm_workspace_bytes(1, M, N, K, &cfg) > kStaticScratchBytes) return B200_ERR_STATIC_SCRATCH;
 
   int dev = 0;
@@ -918,7 +1091,7 @@ int b200_gemm_bf16_gather(int M, int N, int K, const void* A, const void* B, voi
     if (C_all[p] == nullptr) return B200_ERR_INVALID_ARG;
     dst[i] = static_cast<__nv_bfloat16*>(C_all[p]) + static_cast<size_t>(rank) * M * N;
   }
-  b200_gemm_cfg c = cfg ? *cfg : default_cfg(1, M, N, K);
+  b200_gemm_cfg c = cfg ? *cfg : heuristic_cfg(1, M, N, K);
   if (cfg == nullptr) {
     // the fused epilogue exists for 256-column pair tiles with TMA stores
     c.cluster_m = 2;

@@ -14,7 +14,11 @@ What differs from the reference:
     because every GPU minute is budgeted (the reference rewrites a new timestamped JSON after
     every configuration and cannot resume, gemm_tuner.py:128-137);
   * batch mode: `--compile-only DIR` builds one binary per configuration on a machine without a
-    GPU, `--run-only DIR` runs prebuilt binaries on the GPU machine.
+    GPU, `--run-only DIR` runs prebuilt binaries on the GPU machine;
+  * `--shape` may be given several times and `--table FILE` records the best configuration of
+    every shape in the text format `b200_gemm_tuning_load` reads (include/b200_gemm.h), so that
+    what the search finds is what `cfg == NULL` calls use afterwards. The reference's tuner
+    searches one shape and nothing consumes its result (gemm_tuner.py:55,126-145).
 """
 from __future__ import annotations
 
@@ -52,6 +56,35 @@ REFERENCE_PARAM_SPACE = {
     'BLOCKK': [64],
     'STAGES': [3, 5, 7, 9, 11],
 }
+
+TABLE_HEADER = "# batch M N K block_m block_n cluster_m stages sched split_k raster group epilogue\n"
+
+
+def table_line(shape: Tuple[int, int, int], params: Dict[str, int], batch: int = 1) -> str:
+    """One tuning-table entry: the template's parameters for `shape`, data-parallel schedule."""
+    m, n, k = shape
+    return (f"{batch} {m} {n} {k} {params['BLOCKM']} {params['BLOCKN']} {params['CLUSTER_M']} "
+            f"{params['STAGES']} 0 0 0 0 0")
+
+
+def update_table(path, shape: Tuple[int, int, int], params: Dict[str, int], runtime_ms: Optional[float] = None,
+                 batch: int = 1) -> None:
+    """Adds or replaces the entry of `shape` in the table file `path` (created if missing)."""
+    path = Path(path)
+    key = [str(batch)] + [str(v) for v in shape]
+    kept = []
+    if path.exists():
+        for line in path.read_text().splitlines():
+            body = line.split('#', 1)[0].split()
+            if body[:4] == key:
+                continue
+            kept.append(line)
+    if not kept:
+        kept = [TABLE_HEADER.rstrip("\n")]
+    note = f"  # {runtime_ms:.4f} ms" if runtime_ms is not None else ""
+    kept.append(table_line(shape, params, batch) + note)
+    path.write_text("\n".join(kept) + "\n")
+
 
 LATENCY_RE = re.compile(r"Average latency \(ms\) is ([\d.]+)")
 
@@ -203,27 +236,36 @@ def main():
     ap.add_argument("--template", default=str(DEFAULT_TEMPLATE))
     ap.add_argument("--output-dir", default="tuning_results")
     ap.add_argument("--space", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--shape", type=int, nargs=3, default=[5120, 5120, 4096], metavar=("M", "N", "K"))
+    ap.add_argument("--shape", type=int, nargs=3, action="append", metavar=("M", "N", "K"),
+                    help="shape to tune (default 5120 5120 4096); may be repeated")
+    ap.add_argument("--table", metavar="FILE", help="record each shape's best configuration in this tuning table")
     ap.add_argument("--resume", action="store_true")
     ap.add_argument("--compile-only", metavar="DIR")
     ap.add_argument("--run-only", metavar="DIR")
     args = ap.parse_args()
     space = B200_PARAM_SPACE if args.space == "b200" else REFERENCE_PARAM_SPACE
-    tuner = GemmTuner(args.template, args.output_dir, space, tuple(args.shape))
+    shapes = [tuple(sh) for sh in (args.shape or [[5120, 5120, 4096]])]
     if args.compile_only:
+        tuner = GemmTuner(args.template, args.output_dir, space, shapes[0])
         built = tuner.compile_all(args.compile_only)
         print(f"compiled {sum(built.values())}/{len(built)} configurations into {args.compile_only}")
         return
-    best_params, best_runtime, _ = tuner.tune(resume=args.resume, prebuilt_dir=args.run_only)
-    if best_params:
-        print("\nTuning completed!")
-        print(f"Best runtime: {best_runtime:.4f} ms")
-        print("Best parameters:")
-        for key, value in best_params.items():
-            print(f"{key}: {value}")
-        print(f"\nResults saved in {args.output_dir}")
-    else:
-        print("\nNo valid configuration found!")
+    for shape in shapes:
+        out_dir = args.output_dir if len(shapes) == 1 else str(Path(args.output_dir) / "x".join(map(str, shape)))
+        tuner = GemmTuner(args.template, out_dir, space, shape)
+        best_params, best_runtime, _ = tuner.tune(resume=args.resume, prebuilt_dir=args.run_only)
+        if best_params:
+            print("\nTuning completed!")
+            print(f"Best runtime: {best_runtime:.4f} ms")
+            print("Best parameters:")
+            for key, value in best_params.items():
+                print(f"{key}: {value}")
+            print(f"\nResults saved in {out_dir}")
+            if args.table:
+                update_table(args.table, shape, best_params, best_runtime)
+                print(f"Tuning table updated: {args.table}")
+        else:
+            print("\nNo valid configuration found!")
 
 
 if __name__ == "__main__":

@@ -111,6 +111,28 @@ size_t b200_gemm_workspace_bytes(int batch, int M, int N, int K, const b200_gemm
 /* Fills *cfg with the configuration cfg == NULL would use for this shape. */
 int b200_gemm_default_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg);
 
+/* Tuning table: measured configurations fed back into the cfg == NULL dispatch. The reference's
+ * tuner searches one shape and leaves its result in a JSON file and a rendered source
+ * (gemm_tuner.py:126-145); nothing consumes it. Here a table of (batch, M, N, K) -> configuration
+ * is looked up before the built-in heuristic: the exact shape if present, otherwise the entry of
+ * the same class (batched or not; ceil(log2) of M, N and K) nearest in log2 distance.
+ *   b200_gemm_tuning_load   reads a text file — one entry per line,
+ *       batch M N K block_m block_n cluster_m stages sched split_k raster group epilogue
+ *     ('#' starts a comment) — and returns the number of entries added, or -B200_ERR_* when the
+ *     file cannot be read, a line is malformed or names a configuration without a kernel (then
+ *     nothing is added). The environment variable B200_GEMM_TUNING_TABLE names a file that is
+ *     loaded before the first lookup. h100_gemm_b200/tuner/gemm_tuner.py --table writes the format.
+ *   b200_gemm_tuning_add    adds or replaces one entry (c_col_major and max_ctas must be 0: they
+ *     are per-call choices).
+ *   b200_gemm_tuning_clear / _size   empty the table / number of entries.
+ *   b200_gemm_heuristic_cfg the built-in choice, ignoring the table.
+ * b200_gemm_bf16_fixed_scratch and b200_gemm_bf16_gather never consult the table. */
+int b200_gemm_tuning_load(const char* path);
+int b200_gemm_tuning_add(int batch, int M, int N, int K, const b200_gemm_cfg* cfg);
+void b200_gemm_tuning_clear(void);
+int b200_gemm_tuning_size(void);
+int b200_gemm_heuristic_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg);
+
 /* Replaces runKernel(int M,int N,int K,bf16* A,bf16* B,bf16* C,int* DB) —
  * matmul_h100_optimal.cu:32-59: default configuration, COLUMN-major C (ld = M), default stream.
  * DB is accepted and ignored, as in the reference (matmul_h100_optimal.cu:32,58). */
