@@ -2,6 +2,7 @@
 """Headline benchmark: bf16 GEMM C = A * B^T (fp32 accumulate, bf16 out) in TFLOP/s.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py --sweep        # shape sweep beside cuBLAS / cuBLASLt, one JSON line per shape
 
 One step = one pass of the hot path over one synthetic problem:
   * N = 1: M = N = K = 8192, uniform[-1,1] bf16 inputs (the configuration the headline metric is
@@ -241,6 +242,101 @@ def run_reference(args):
 # --------------------------------------------------------------------------------------------
 # Our arm
 # --------------------------------------------------------------------------------------------
+SWEEP_SHAPES = [
+    # (name, M, N, K, generator of A, generator of B)
+    ("square1024", 1024, 1024, 1024, "uniform", "uniform"),
+    ("square2048", 2048, 2048, 2048, "uniform", "uniform"),
+    ("square4096", 4096, 4096, 4096, "uniform", "uniform"),
+    ("tuner5120x5120x4096", 5120, 5120, 4096, "uniform", "uniform"),
+    ("square6144", 6144, 6144, 6144, "uniform", "uniform"),
+    ("square8192", 8192, 8192, 8192, "uniform", "uniform"),
+    ("square16384", 16384, 16384, 16384, "uniform", "uniform"),
+    ("prefill8192x28672x8192", 8192, 28672, 8192, "normal", "normal0.02"),
+    ("ragged3000x1000x5555", 3000, 1000, 5555, "uniform", "uniform"),
+    ("skinny16", 16, 28672, 8192, "normal", "normal0.02"),
+    ("skinny32", 32, 28672, 8192, "normal", "normal0.02"),
+    ("skinny64", 64, 28672, 8192, "normal", "normal0.02"),
+    ("skinny128", 128, 28672, 8192, "normal", "normal0.02"),
+]
+
+
+def run_sweep(args):
+    """One GPU, kernel-only: this library (cfg = NULL dispatch) beside cuBLAS and cuBLASLt on the same
+    buffers over a list of shapes; one JSON line per shape. Operand sets rotate so that the bytes
+    touched between two uses of a buffer exceed twice the L2 capacity; the three implementations
+    are timed in interleaved rounds (the median round is reported) so that clock drift under the
+    power cap hits them alike."""
+    import statistics
+
+    import torch
+    import h100_gemm_b200 as g
+    from h100_gemm_b200 import baselines
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the GEMM has no CPU fallback")
+    g.library()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks = measured_peaks()
+    stream = torch.cuda.current_stream()
+    for name, M, N, K, ka, kb in SWEEP_SHAPES:
+        set_bytes = 2 * (M * K + N * K + M * N)
+        sets = max(1, min(64, -(-2 * 126_000_000 // set_bytes)))
+        ops = []
+        for i in range(sets):
+            a, b = make_inputs(torch, M, N, K, ka, kb, seed=7 + i, device=device)
+            ops.append((a, b, torch.empty(M, N, dtype=torch.bfloat16, device=device)))
+        cfg = g.default_config(1, M, N, K)
+        ws = torch.empty(max(g.workspace_bytes(1, M, N, K, cfg), 1), dtype=torch.uint8, device=device)
+        impls = {
+            "ours": lambda a, b, c: g.gemm(a, b, out=c, cfg=cfg, workspace=ws, stream=stream),
+            "cublas_gemm_ex": lambda a, b, c: baselines.cublas_gemm(a, b, out=c),
+            "cublaslt_matmul": lambda a, b, c: baselines.cublaslt_gemm(a, b, out=c),
+        }
+        flops = 2.0 * M * N * K
+        iters = max(5, min(200, int(0.02 / max(flops / 1.5e15, set_bytes / 6e12))))
+        rounds = {k: [] for k in impls}
+        for rnd in range(5):
+            for k, fn in impls.items():
+                for i in range(3):
+                    fn(*ops[i % sets])
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for i in range(iters):
+                    fn(*ops[i % sets])
+                e1.record(stream)
+                torch.cuda.synchronize()
+                rounds[k].append(e0.elapsed_time(e1) / iters)
+        rc, words = g.device_status()
+        if rc != 0:
+            raise SystemExit(f"device status {words}")
+        # same bits as cuBLAS is not required (different K order); agreement within bf16 rounding is
+        a, b, c = ops[0]
+        impls["ours"](a, b, c)
+        mine = c.float()
+        impls["cublas_gemm_ex"](a, b, c)
+        torch.cuda.synchronize()
+        scale = a.float().norm(dim=1).max() * b.float().norm(dim=1).max()
+        err = float((mine - c.float()).abs().max() / scale)
+        ms = {k: statistics.median(v) for k, v in rounds.items()}
+        hbm = M <= 128
+        line = {"shape": name, "M": M, "N": N, "K": K, "operand_sets": sets, "iters_per_round": iters, "rounds": 5,
+                "config": {"block_m": cfg.block_m, "block_n": cfg.block_n, "cluster_m": cfg.cluster_m,
+                           "stages": cfg.stages, "sched": cfg.sched},
+                "ms": ms, "ours_over_cublas_time": ms["ours"] / ms["cublas_gemm_ex"],
+                "ours_over_cublaslt_time": ms["ours"] / ms["cublaslt_matmul"],
+                "max_err_vs_cublas_norm_relative": err}
+        if hbm:
+            line["ours_gbs"] = set_bytes / (ms["ours"] * 1e-3) / 1e9
+            line["frac_of_hbm_peak"] = line["ours_gbs"] / peaks["hbm_gbs"]
+        else:
+            line["ours_tflops"] = flops / (ms["ours"] * 1e-3) / 1e12
+            line["frac_of_bf16_burst_peak"] = line["ours_tflops"] / peaks["burst"]
+        line["peaks"] = peaks["source"]
+        print(json.dumps(line), flush=True)
+        del ops, ws
+        torch.cuda.empty_cache()
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -477,11 +573,16 @@ def main():
                     help="N > 1: also time the variant that all-gathers C over NCCL (reported separately)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for profiler captures)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="one GPU, kernel-only: this library beside cuBLAS and cuBLASLt over a list of shapes, "
+                         "one JSON line per shape (not the headline line)")
     args = ap.parse_args()
     if args.steps < 1 or args.warmup < 0:
         raise SystemExit("--steps must be >= 1 and --warmup >= 0")
     if args.impl == "reference":
         return run_reference(args)
+    if args.sweep:
+        return run_sweep(args)
     return run_ours(args)
 
 
