@@ -102,6 +102,25 @@ def test_comparison_harnesses_run():
 
 
 @pytest.mark.gpu
+def test_cutlass_comparator_agrees_bit_for_bit():
+    """The CUTLASS Sm100 builder GEMM, this library and the SIMT GEMM give the same bits on
+    integer-valued inputs (the harness exits non-zero otherwise). Needs CUTLASS 4.x headers at
+    build time; skipped where there are none and no prebuilt binary."""
+    binary = REPO / "h100_gemm_b200" / "bench" / "bin" / "cutlass_ref"
+    source = REPO / "h100_gemm_b200" / "bench" / "cutlass_ref.cu"
+    if not binary.exists() or binary.stat().st_mtime < source.stat().st_mtime:
+        made = subprocess.run(["make", "-C", str(REPO / "h100_gemm_b200" / "bench"), "cutlass_ref"], capture_output=True,
+                              text=True, timeout=900)
+        if made.returncode != 0:
+            pytest.skip("CUTLASS headers not available: " + made.stdout[-200:])
+    out = subprocess.run([str(binary), "--m=1024", "--n=768", "--k=512", "--iterations=5"], capture_output=True,
+                         text=True, timeout=120)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert out.stdout.count("Disposition: Passed") == 2 and out.stdout.count("GFLOPS:") == 2
+    assert "CUTLASS 0, libb200gemm 0" in out.stdout
+
+
+@pytest.mark.gpu
 def test_vendor_baselines_agree_with_the_kernel():
     import torch
 
