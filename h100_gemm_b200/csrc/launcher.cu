@@ -427,7 +427,7 @@ int resolve_plan(const b200_gemm_cfg& c, Plan* p) {
   if (p->stages > kMaxStages) return B200_ERR_UNSUPPORTED_CFG;
   if (p->stages == 1) return B200_ERR_UNSUPPORTED_CFG;
   p->smem = 0;
-  if (c.sched < 0 || c.sched > 3) return B200_ERR_INVALID_ARG;
+  if (c.sched < 0 || c.sched > 4) return B200_ERR_INVALID_ARG;
   p->mode = c.sched;
   p->split_k = c.split_k <= 1 ? 1 : c.split_k;
   if (p->split_k > 64) return B200_ERR_UNSUPPORTED_CFG;
@@ -659,7 +659,9 @@ void build_sched(const Plan& p, const Problem& pr, int workers, SchedParams* s) 
     s->mode = kDataParallel;
     s->split_k = 1;
   }
-  if (s->mode == kHybrid && s->num_tiles <= workers) s->mode = kDataParallel;  // no full wave to keep whole
+  if ((s->mode == kHybrid || s->mode == kHybridTwoWaves) && s->num_tiles <= workers) {
+    s->mode = kDataParallel;  // a single wave: nothing to balance against
+  }
   long long units = s->num_tiles;
   if (s->mode == kSplitK) units *= s->split_k;
   if (s->mode == kStreamK) units = sched_total_iters(*s);
@@ -670,7 +672,7 @@ void build_sched(const Plan& p, const Problem& pr, int workers, SchedParams* s) 
 WorkspaceLayout workspace_layout(const Plan& p, const Problem& pr, const SchedParams& s) {
   WorkspaceLayout w{};
   const int block_m = p.kernel->block_m;
-  w.flag_bytes = (s.mode == kStreamK || s.mode == kHybrid) ? align_up(static_cast<size_t>(sched_num_slots(s)) * 16 * sizeof(unsigned long long), 256) : 0;
+  w.flag_bytes = sched_has_streamk_part(s.mode) ? align_up(static_cast<size_t>(sched_num_slots(s)) * 16 * sizeof(unsigned long long), 256) : 0;
   w.partial_bytes =
       align_up(static_cast<size_t>(sched_num_slots(s)) * block_m * p.kernel->bn * sizeof(float), 256);
   w.repitch = needs_repitch(pr);

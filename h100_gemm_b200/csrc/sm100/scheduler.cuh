@@ -10,6 +10,10 @@
 //   mode 3  hybrid        : the full waves of tiles run data-parallel; only the tiles of the last,
 //                           partly filled wave are cut stream-K style, so every worker finishes at
 //                           the same time without paying for partial tiles on the full waves
+//   mode 4  hybrid, two waves : as mode 3, but the last FULL wave is cut stream-K style together
+//                           with the partly filled one, so every worker's share is at least one
+//                           tile long and a tile has at most three contributors however few tiles
+//                           the last wave holds
 // Partial segments carry a slot index into an fp32 workspace. Split-K slots are summed in slot
 // order by a fix-up pass. Under stream-K a tile cut across workers is finished inside the GEMM
 // kernel: the worker holding the tile's head (k_begin == 0) adds the partial tiles of the workers
@@ -31,7 +35,11 @@
 
 namespace b200 {
 
-enum SchedMode : int { kDataParallel = 0, kSplitK = 1, kStreamK = 2, kHybrid = 3 };
+enum SchedMode : int { kDataParallel = 0, kSplitK = 1, kStreamK = 2, kHybrid = 3, kHybridTwoWaves = 4 };
+
+B200_SCHED_HD bool sched_has_streamk_part(int mode) {
+  return mode == kStreamK || mode == kHybrid || mode == kHybridTwoWaves;
+}
 
 struct SchedParams {
   int tiles_m;      // output tiles along M
@@ -91,6 +99,11 @@ B200_SCHED_HD long long sched_total_iters(const SchedParams& p) {
 B200_SCHED_HD int streamk_tile_base(const SchedParams& p) {
   if (p.mode == kStreamK) return 0;
   if (p.mode == kHybrid) return (p.num_tiles / p.num_workers) * p.num_workers;
+  if (p.mode == kHybridTwoWaves) {
+    const int full = p.num_tiles / p.num_workers;
+    if (full * p.num_workers == p.num_tiles) return p.num_tiles;  // no partly filled wave: nothing to cut
+    return (full > 0 ? full - 1 : 0) * p.num_workers;
+  }
   return p.num_tiles;
 }
 
@@ -112,7 +125,7 @@ B200_SCHED_HD int splitk_begin(const SchedParams& p, int s) {
 // Number of fp32 partial slots the workspace must hold.
 B200_SCHED_HD long long sched_num_slots(const SchedParams& p) {
   if (p.mode == kSplitK) return p.split_k > 1 ? static_cast<long long>(p.split_k) * p.num_tiles : 0;
-  if (p.mode == kStreamK || p.mode == kHybrid) {
+  if (sched_has_streamk_part(p.mode)) {
     return streamk_iters(p) > 0 ? p.num_workers : 0;  // one per worker: its first stream-K segment
   }
   return 0;

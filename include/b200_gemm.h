@@ -45,7 +45,8 @@ typedef enum b200_status {
  *   cluster_n must be 1 (the reference's tuner rejects anything else, gemm_tuner.py:77-78).
  * The rest are additions with neutral defaults (all zero):
  *   sched     0 data-parallel tiles, 1 split-K, 2 stream-K, 3 hybrid (full waves of tiles
- *             data-parallel, the last partly filled wave stream-K).
+ *             data-parallel, the last partly filled wave stream-K), 4 hybrid over two waves (the
+ *             last full wave is cut stream-K style together with the partly filled one).
  *   split_k   K-slices per tile for sched 1 (0/1 = none).
  *   raster    0 group tiles along M, 1 along N.
  *   group     raster group width in tiles; 0 = default (8).

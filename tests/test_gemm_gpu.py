@@ -208,7 +208,10 @@ def test_skinny_decode(g, skinny_b, m):
                                     dict(block_m=256, block_n=128, cluster_m=1, sched=1, split_k=2),
                                     dict(block_n=64, cluster_m=1, sched=3),
                                     dict(block_n=128, cluster_m=2, sched=3, max_ctas=16),
-                                    dict(block_m=256, block_n=128, cluster_m=1, sched=3, max_ctas=5)])
+                                    dict(block_m=256, block_n=128, cluster_m=1, sched=3, max_ctas=5),
+                                    dict(block_n=128, cluster_m=1, sched=4, max_ctas=20),
+                                    dict(block_n=256, cluster_m=2, sched=4, max_ctas=10),
+                                    dict(block_m=256, block_n=256, cluster_m=2, sched=4, max_ctas=6)])
 def test_split_and_stream_k_integer_exact(g, cfg_kw):
     from h100_gemm_b200.api import GemmConfig as C
     M, N, K = 700, 900, 3000

@@ -67,11 +67,23 @@ def test_tile_coord_is_a_bijection(shim, tm, tn, batch, group, raster):
     assert len(seen) == tm * tn * batch
 
 
+def streamk_base(mode, tiles, workers):
+    """First tile of the part that is cut stream-K style."""
+    full = tiles // workers
+    if mode == 2:
+        return 0
+    if mode == 3:
+        return full * workers
+    if full * workers == tiles:
+        return tiles                       # mode 4 without a partly filled wave: all tiles stay whole
+    return max(full - 1, 0) * workers
+
+
 CASES = [(4, 4, 1, 16), (32, 32, 1, 128), (1, 224, 1, 128), (3, 5, 2, 9), (1, 1, 1, 1), (1, 3, 1, 200), (7, 3, 1, 2)]
 
 
 @pytest.mark.parametrize("tm,tn,batch,kt", CASES)
-@pytest.mark.parametrize("mode,split", [(0, 1), (1, 2), (1, 3), (1, 5), (2, 1), (3, 1)])
+@pytest.mark.parametrize("mode,split", [(0, 1), (1, 2), (1, 3), (1, 5), (2, 1), (3, 1), (4, 1)])
 @pytest.mark.parametrize("workers", [1, 7, 74, 148])
 def test_every_k_iteration_is_visited_exactly_once(shim, tm, tn, batch, kt, mode, split, workers):
     tiles = tm * tn * batch
@@ -79,8 +91,8 @@ def test_every_k_iteration_is_visited_exactly_once(shim, tm, tn, batch, kt, mode
         split = min(split, kt)
         if split <= 1:
             mode, split = 0, 1
-    if mode == 3 and tiles <= workers:
-        mode = 0  # what the launcher does: no full wave to keep whole
+    if mode in (3, 4) and tiles <= workers:
+        mode = 0  # what the launcher does: a single wave has nothing to balance against
     units = tiles * (split if mode == 1 else 1) if mode != 2 else tiles * kt
     workers = min(workers, units)
     visits = defaultdict(int)
@@ -97,10 +109,10 @@ def test_every_k_iteration_is_visited_exactly_once(shim, tm, tn, batch, kt, mode
             full = kb == 0 and ke == kt
             if mode == 0:
                 assert slot < 0 and finish == 0
-            if mode in (2, 3):
+            if mode in (2, 3, 4):
                 # partials are contributed only by a worker's first stream-K segment, into its own
                 # slot; the holder of the tile's head finishes it
-                base = 0 if mode == 2 else (tiles // workers) * workers
+                base = streamk_base(mode, tiles, workers)
                 first_sk = next((j for j, sg in enumerate(segs) if sg[0] >= base), None)
                 assert (slot >= 0) == (kb > 0) and (slot < 0 or (slot == w and i == first_sk))
                 if tile < base:
@@ -121,9 +133,9 @@ def test_every_k_iteration_is_visited_exactly_once(shim, tm, tn, batch, kt, mode
             n = shim.hs_tile_slots(tm, tn, batch, kt, mode, split, workers, tile, buf, 64)
             assert n <= 64
             assert [buf[i] for i in range(n)] == [s for _, s in sorted(slots_by_tile[tile])]
-    if mode in (2, 3):
+    if mode in (2, 3, 4):
         # every finisher's contributors are the next workers' first segments and tile the rest of K
-        base = 0 if mode == 2 else (tiles // workers) * workers
+        base = streamk_base(mode, tiles, workers)
         first = ctypes.c_int()
         for w, segs in per_worker.items():
             for tile, kb, ke, slot, finish in segs:
