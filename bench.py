@@ -400,6 +400,36 @@ def run_ours(args):
     ms_total = float(t.item())
     ms_step = ms_total / args.steps
 
+    # ---- sustained: the same step back to back for at least two seconds, timed in chunks ----
+    # (The headline region above is a burst well under a second; under the 1 kW cap the clock settles
+    # lower after a second or so. Reported beside the headline, against the sustained cuBLAS peak.)
+    sustained = None
+    if not args.kernel_only:
+        import statistics
+        chunk = max(5, int(100.0 / ms_step))                       # about 0.1 s of launches
+        n_chunks = max(4, int(2200.0 / (chunk * ms_step)) + 1)
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(n_chunks + 1)]
+        barrier()
+        with ClockSampler(physical_gpu_index(local)) as s_clocks:
+            marks[0].record(stream)
+            for ci in range(n_chunks):
+                for i in range(chunk):
+                    step(i)
+                marks[ci + 1].record(stream)
+            torch.cuda.synchronize()
+        per_chunk = [marks[i].elapsed_time(marks[i + 1]) / chunk for i in range(n_chunks)]
+        tail = per_chunk[len(per_chunk) // 2:]                     # the second half: after the clock has settled
+        stats = torch.tensor([marks[0].elapsed_time(marks[-1]), statistics.median(tail), min(per_chunk)],
+                             dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        sustained = {"seconds": float(stats[0]) / 1e3, "launches": chunk * n_chunks,
+                     "ms_per_step_settled_median": float(stats[1]), "ms_per_step_best_chunk": float(stats[2]),
+                     "clocks": s_clocks.summary()}
+        rc, words = g.device_status()
+        if rc != 0:
+            raise SystemExit(f"device status {words}")
+
     # ---- vendor baselines on the same buffers (reported next to the result, not a target) ----
     vendor = None
     if world == 1 and not args.kernel_only:
@@ -545,6 +575,15 @@ def run_ours(args):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary(),
         }
+        if sustained is not None:
+            per = (bytes_step / 1e9) if hbm else (flops_step / 1e12)
+            sustained["value"] = world * per / (sustained["ms_per_step_settled_median"] * 1e-3)
+            sustained["unit"] = unit
+            peak = peaks["hbm_gbs"] if hbm else peaks["sustained"]
+            sustained["frac_of_peak"] = sustained["value"] / world / peak
+            sustained["peak"] = peak
+            sustained["peak_source"] = f"{peaks['source']} " + ("copy bandwidth" if hbm else "cuBLAS bf16 sustained")
+            line["sustained"] = sustained
         if gathered is not None:
             line["with_allgather"] = gathered
         if vendor is not None:
