@@ -27,3 +27,22 @@ def test_reference_arm_is_silent_on_other_ranks():
     out = subprocess.run([sys.executable, str(REPO / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
                           "--warmup", "0"], capture_output=True, text=True, timeout=60, env=env)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+import pytest
+
+
+@pytest.mark.gpu
+def test_own_arm_prints_the_contract_line_on_a_gpu():
+    out = subprocess.run([sys.executable, str(REPO / "bench.py"), "--steps", "3", "--warmup", "3", "--workload",
+                          "square4096", "--kernel-only"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-800:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "roofline", "gpu_launches", "clocks"):
+        assert key in line, key
+    assert line["n_gpus"] == 1 and line["steps"] == 3 and line["gpu_launches"] == 3 and line["dtype"] == "bf16"
+    roof = line["roofline"]
+    assert roof["bound"] == "tensor" and roof["unit"] == "TFLOP/s"
+    assert abs(roof["frac"] - roof["achieved"] / roof["peak"]) < 1e-9 and 0.05 < roof["frac"] < 1.3
+    assert "workload" in line["config"] and "model" not in line["config"]
