@@ -194,6 +194,7 @@ KernelEntry make_entry() {
 
 const KernelEntry* find_kernel(int bn, int pair, int mt) {
   static const KernelEntry table[] = {
+      make_entry<16, 0, 1>(),  make_entry<32, 0, 1>(),
       make_entry<64, 0, 1>(),  make_entry<128, 0, 1>(), make_entry<192, 0, 1>(), make_entry<256, 0, 1>(),
       make_entry<64, 1, 1>(),  make_entry<128, 1, 1>(), make_entry<192, 1, 1>(), make_entry<256, 1, 1>(),
       make_entry<128, 0, 2>(), make_entry<256, 0, 2>(), make_entry<128, 1, 2>(), make_entry<256, 1, 2>(),
@@ -351,6 +352,7 @@ struct Plan {
   int max_ctas;
   int c_col_major;
   int store_mode;  // StoreMode to use when C is 16-byte aligned
+  int few_rows;    // 1: block_m < 128 — the caller's rows ride the MMA's N (operands swapped inside)
 };
 
 // Default configuration from the shape. For M > 128 the candidates are ranked by a small cost
@@ -364,6 +366,18 @@ b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K) {
   c.block_k = 64;
   c.cluster_n = 1;
   c.group = 8;
+  if (M <= 64 && N >= 128) {
+    // Very few rows: let them ride the MMA's N dimension (block_m = 16, 32 or 64) and put 128 rows
+    // of B on its M dimension. The tensor cores then compute block_m x 128 per tile instead of a
+    // 128-row tile that is mostly padding — an eighth of the tensor work at M = 16, which matters
+    // because this shape runs into the power cap long before it runs out of HBM bandwidth. The K
+    // loop is split evenly over all SMs (stream-K) so that every SM streams the same share of B.
+    c.cluster_m = 1;
+    c.block_m = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    c.block_n = 128;
+    c.sched = kStreamK;
+    return c;
+  }
   if (M <= 128) {
     // Few rows: one CTA per tile, narrower tiles, and an even split of the K loop over all SMs
     // so that every SM streams the same share of B.
@@ -413,14 +427,26 @@ b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K) {
 
 int resolve_plan(const b200_gemm_cfg& c, Plan* p) {
   if (c.block_k != 0 && c.block_k != 64) return B200_ERR_UNSUPPORTED_CFG;
-  if (c.block_m != 0 && c.block_m != 128 && c.block_m != 256) return B200_ERR_UNSUPPORTED_CFG;
-  const int mt = c.block_m == 256 ? 2 : 1;
   if (c.cluster_n != 0 && c.cluster_n != 1) return B200_ERR_UNSUPPORTED_CFG;
   int cm = c.cluster_m == 0 ? 1 : c.cluster_m;
   if (cm < 1 || cm > 16 || (cm & (cm - 1)) != 0) return B200_ERR_UNSUPPORTED_CFG;
-  const int bn = c.block_n == 0 ? 128 : c.block_n;
-  p->pair = cm >= 2 ? 1 : 0;
-  p->kernel = find_kernel(bn, p->pair, mt);
+  p->few_rows = 0;
+  if (c.block_m == 16 || c.block_m == 32 || c.block_m == 64) {
+    // Few-rows plan: a block_m x 128 tile computed with the operands swapped — 128 rows of B on the
+    // MMA's M dimension, block_m rows of A on its N dimension — and stored transposed. Single CTA.
+    if ((c.block_n != 0 && c.block_n != 128) || cm != 1) return B200_ERR_UNSUPPORTED_CFG;
+    if (c.sched == kSplitK) return B200_ERR_UNSUPPORTED_CFG;  // the fix-up pass writes whole rows of C
+    p->few_rows = 1;
+    p->pair = 0;
+    p->kernel = find_kernel(c.block_m, 0, 1);
+  } else {
+    if (c.block_m != 0 && c.block_m != 128 && c.block_m != 256) return B200_ERR_UNSUPPORTED_CFG;
+    const int mt = c.block_m == 256 ? 2 : 1;
+    const int bn = c.block_n == 0 ? 128 : c.block_n;
+    if (bn < 64) return B200_ERR_UNSUPPORTED_CFG;  // the narrow kernels serve the few-rows plan only
+    p->pair = cm >= 2 ? 1 : 0;
+    p->kernel = find_kernel(bn, p->pair, mt);
+  }
   if (p->kernel == nullptr) return B200_ERR_UNSUPPORTED_CFG;
   if (c.stages < 0) return B200_ERR_INVALID_ARG;
   p->stages = c.stages;  // 0 = as many as fit; settled by fit_stages() once the A tile is known
@@ -440,6 +466,7 @@ int resolve_plan(const b200_gemm_cfg& c, Plan* p) {
                                                                                                 : kStoreTma;
   p->max_ctas = c.max_ctas;
   p->c_col_major = c.c_col_major ? 1 : 0;
+  if (p->few_rows) p->store_mode = kStoreScalar;  // transposed (or 16/32-column) stores: no TMA staging
   return B200_OK;
 }
 
@@ -610,7 +637,10 @@ b200_gemm_cfg default_cfg(int batch, int M, int N, int K) {
     // leaves room for: then take as many as fit.
     Plan plan;
     if (resolve_plan(c, &plan) == B200_OK) {
-      if (fit_stages(&plan, a_rows_for(plan, M), epi_bytes_for(plan, plan.store_mode)) != B200_OK) c.stages = 0;
+      if (fit_stages(&plan, a_rows_for(plan, plan.few_rows ? N : M), epi_bytes_for(plan, plan.store_mode)) !=
+          B200_OK) {
+        c.stages = 0;
+      }
       return c;
     }
   }
@@ -723,8 +753,14 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   if (rc != B200_OK) return rc;
 
   Problem pr{batch, M, N, K, A, B, C, strideA, strideB, strideC};
-  if (plan.c_col_major) {
-    // Column-major C[M,N] (ld M) is row-major C^T[N,M] = B * A^T: swap the operands.
+  // The kernel computes P[pr.M, pr.N] = pr.A * pr.B^T. Two things swap the operands:
+  //  * column-major C[M,N] (ld M) is row-major C^T[N,M] = B * A^T;
+  //  * the few-rows plan puts the caller's rows on the MMA's N dimension, so the kernel computes
+  //    C^T as well — and stores it transposed, which makes it the caller's row-major C again.
+  // Both at once: the kernel's product C^T is what a column-major C holds, stored as it is.
+  const bool swap_operands = plan.c_col_major || plan.few_rows;
+  const int c_transposed = (plan.few_rows && !plan.c_col_major) ? 1 : 0;
+  if (swap_operands) {
     pr.M = N;
     pr.N = M;
     pr.A = B;
@@ -737,7 +773,7 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   // batch pitch are 16-byte aligned; otherwise the epilogue falls back to 2-byte stores.
   const bool c_aligned = (pr.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(pr.C) & 15u) == 0) &&
                          (pr.batch == 1 || pr.strideC % 8 == 0);
-  const int store_mode = !c_aligned ? kStoreScalar : plan.store_mode;
+  const int store_mode = (!c_aligned || plan.few_rows) ? kStoreScalar : plan.store_mode;
   const int epi_bytes = epi_bytes_for(plan, store_mode);
   const int a_rows = a_rows_for(plan, pr.M);
   rc = fit_stages(&plan, a_rows, epi_bytes);
@@ -829,7 +865,8 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   args.store_mode = store_mode;
   args.epi_bytes = epi_bytes;
   args.C = static_cast<__nv_bfloat16*>(pr.C);
-  args.ldc = pr.N;
+  args.ldc = c_transposed ? pr.M : pr.N;
+  args.c_transposed = c_transposed;
   args.c_batch_stride = pr.strideC;
   args.flags = ws.flag_bytes ? static_cast<unsigned long long*>(workspace) : nullptr;
   args.partial = ws.partial_bytes
@@ -947,7 +984,7 @@ size_t b200_gemm_workspace_bytes(int batch, int M, int N, int K, const b200_gemm
   if (resolve_plan(cfg, &plan) != B200_OK) return 0;
   Problem pr{batch, M, N, K, reinterpret_cast<const void*>(16), reinterpret_cast<const void*>(16),
              nullptr, 8, 8, 8};
-  if (plan.c_col_major) {
+  if (plan.c_col_major || plan.few_rows) {
     pr.M = N;
     pr.N = M;
   }
@@ -972,7 +1009,8 @@ int b200_gemm_default_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg) {
   Plan plan;
   int rc = resolve_plan(*cfg, &plan);
   if (rc != B200_OK) return rc;
-  rc = fit_stages(&plan, a_rows_for(plan, M), epi_bytes_for(plan, N % 8 == 0 ? plan.store_mode : kStoreScalar));
+  rc = fit_stages(&plan, a_rows_for(plan, plan.few_rows ? N : M),
+                  epi_bytes_for(plan, N % 8 == 0 ? plan.store_mode : kStoreScalar));
   if (rc != B200_OK) return rc;
   cfg->stages = plan.stages;
   return B200_OK;
@@ -1015,7 +1053,15 @@ int b200_gemm_heuristic_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg) 
 int b200_run_kernel(int M, int N, int K, void* A, void* B, void* C, int* DB) {
   (void)DB;
   if (M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARG;
-  b200_gemm_cfg cfg = default_cfg(1, N, M, K);  // shape as the kernel sees it after the swap
+  // Column-major C: the kernel computes C^T[N, M], so the shape it sees is (N, M) — except that
+  // block_m < 128 always counts the CALLER's rows (they ride the MMA's N dimension).
+  b200_gemm_cfg cfg;
+  if (M <= 64 && N >= 128) {
+    cfg = heuristic_cfg(1, M, N, K);  // few caller rows
+  } else {
+    cfg = default_cfg(1, N, M, K);
+    if (cfg.block_m < 128) cfg = heuristic_cfg(1, 128, M, K);  // few kernel rows (small N): short A tile
+  }
   cfg.sched = kDataParallel;
   cfg.c_col_major = 1;
   return run_gemm(1, M, N, K, A, 0, B, 0, C, 0, 1.0f, 0.0f, &cfg, nullptr, 0, nullptr);

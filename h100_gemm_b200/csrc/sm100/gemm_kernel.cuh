@@ -99,12 +99,16 @@ struct GemmArgs {
   int a_stage_bytes;          // a_rows * 128
   float alpha, beta;
   int scale;                  // 1: C = acc * alpha + beta (the scalar-beta rule of reference.h:40)
+  int c_transposed;           // 1: element (row, col) of the kernel's product goes to C[col * ldc + row]
+                              //    (few-rows plan: the caller's rows ride the MMA's N; BN <= 64 kernels only)
   unsigned int* status;       // 4 words: code, block, tile, detail
 };
 
 template <int BN, int PAIR, int MT>
 struct KernelTraits {
-  static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN must be 64, 128, 192 or 256");
+  static_assert(BN == 16 || BN == 32 || (BN % 64 == 0 && BN >= 64 && BN <= 256),
+                "BN must be 16, 32, 64, 128, 192 or 256");
+  static_assert(BN >= 64 || (PAIR == 0 && MT == 1), "narrow tiles are single-CTA, one sub-tile");
   static_assert(MT == 1 || MT == 2, "one or two 128-row sub-tiles of A per CTA");
   static constexpr int kCtaGroup = PAIR ? 2 : 1;
   static constexpr int kUmmaM = kCtaRows * kCtaGroup;         // rows of one tcgen05.mma
@@ -478,6 +482,79 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
       }
 
+      if constexpr (BN < kEpiChunkCols) {
+        // Narrow tile (16 or 32 columns): one tensor-memory read is the warp's whole share, so the
+        // accumulator buffer goes back to the MMA issuer before anything is stored.
+        const int m_slab = tc.m * T::kBlockM + q * 32;     // this warp's first row (single CTA, MT = 1)
+        const int row_in_tile = q * 32 + static_cast<int>(lane);
+        const int row = m_slab + static_cast<int>(lane);
+        const bool row_live = row < args.M;
+        const bool live = m_slab < args.M;                  // warp-uniform
+        uint32_t v[BN];
+        if (live) {
+          ptx::tmem_ld_cols(tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                static_cast<uint32_t>(acc * T::kAccCols),
+                            v);
+          ptx::tmem_ld_wait();
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(tmem_empty_leader + 8u * static_cast<uint32_t>(acc));
+        if (prof_epi) epi_drain += clock64() - te1;
+        // fp32 partial tile of a narrow kernel: [4-column piece][row (128)][4 floats], so the 32
+        // lanes of a warp write 512 contiguous bytes per store instruction.
+        constexpr int kPieceStride = kCtaRows * 4;
+        if (live && row_live) {
+          if (to_slot) {
+            float* dst = args.partial + static_cast<long long>(seg.slot) * (T::kBlockM * BN) + row_in_tile * 4;
+#pragma unroll
+            for (int j = 0; j < BN; j += 4) {
+              __stcg(reinterpret_cast<float4*>(dst + (j / 4) * kPieceStride),
+                     make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                 __uint_as_float(v[j + 3])));
+            }
+          } else {
+            for (int w = 0; w < contrib_count; ++w) {
+              const float* src =
+                  args.partial + static_cast<long long>(contrib_first + w) * (T::kBlockM * BN) + row_in_tile * 4;
+#pragma unroll
+              for (int j = 0; j < BN; j += 4) {
+                const float4 f = __ldcg(reinterpret_cast<const float4*>(src + (j / 4) * kPieceStride));
+                v[j + 0] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 0]), f.x));
+                v[j + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 1]), f.y));
+                v[j + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 2]), f.z));
+                v[j + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 3]), f.w));
+              }
+            }
+            if (args.scale) {
+#pragma unroll
+              for (int j = 0; j < BN; ++j) {
+                v[j] = __float_as_uint(__fadd_rn(__fmul_rn(__uint_as_float(v[j]), args.alpha), args.beta));
+              }
+            }
+            uint16_t* cbase = reinterpret_cast<uint16_t*>(args.C) + tc.b * args.c_batch_stride;
+            if (args.c_transposed) {
+              // column j of the product is a row of the caller's C: the warp's lanes write 32
+              // consecutive 16-bit elements of it
+#pragma unroll
+              for (int j = 0; j < BN; ++j) {
+                if (n_tile + j < args.N) {
+                  cbase[static_cast<long long>(n_tile + j) * args.ldc + row] =
+                      static_cast<uint16_t>(pack16<F16>(__uint_as_float(v[j]), 0.0f) & 0xFFFFu);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN; ++j) {
+                if (n_tile + j < args.N) {
+                  cbase[static_cast<long long>(row) * args.ldc + n_tile + j] =
+                      static_cast<uint16_t>(pack16<F16>(__uint_as_float(v[j]), 0.0f) & 0xFFFFu);
+                }
+              }
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < kChunksPerSub; ++c) {  // 64-column chunks of this warp's sub-tile
         const int tile_row = cta_row0 + mt * kCtaRows + q * 32;  // this warp's first row in the tile
@@ -608,6 +685,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                   *reinterpret_cast<uint4*>(dst + h * 32 + j * 8) = w;
                 }
               }
+            } else if (BN <= kEpiChunkCols && args.c_transposed) {
+              // few-rows plan: column j of the product is a row of the caller's C
+              uint16_t* cbase = reinterpret_cast<uint16_t*>(args.C) + tc.b * args.c_batch_stride +
+                                (m_slab + static_cast<int>(lane));
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (n0 + h * 32 + j < args.N) {
+                    cbase[static_cast<long long>(n0 + h * 32 + j) * args.ldc] =
+                        static_cast<uint16_t>(pack16<F16>(__uint_as_float(v[h][j]), 0.0f) & 0xFFFFu);
+                  }
+                }
+              }
             } else {
 #pragma unroll
               for (int h = 0; h < 2; ++h) {
@@ -655,6 +746,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         ++store_count;
       }
+      }  // wide tiles
       if (prof_epi) {
         epi_busy += clock64() - te1;
         ++epi_tiles;

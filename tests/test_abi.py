@@ -72,8 +72,15 @@ def test_default_config(lib):
     c = api.default_config(1, 8192, 8192, 8192)
     assert (c.block_m, c.block_n, c.block_k, c.cluster_m, c.cluster_n) == (256, 256, 64, 2, 1)
     assert c.stages >= 3
+    # decode shape: the 16 rows ride the MMA's N (16 x 128 tiles), K split evenly over the SMs
     s = api.default_config(1, 16, 28672, 8192)
-    assert s.sched == 2 and s.cluster_m == 1 and s.stages >= 16
+    assert (s.block_m, s.block_n, s.sched, s.cluster_m) == (16, 128, 2, 1) and s.stages == 12
+    assert api.default_config(1, 33, 28672, 8192).block_m == 64
+    # 65..128 rows keep 128-row tiles with a short A stage
+    t = api.default_config(1, 100, 28672, 8192)
+    assert (t.block_m, t.sched, t.cluster_m) == (128, 2, 1)
+    # few-rows stream-K workspace: one 128 x 16 fp32 slot and 16 flag words per SM
+    assert api.workspace_bytes(1, 16, 28672, 8192, None) == 148 * 128 * 16 * 4 + 148 * 128
     with pytest.raises(api.GemmError):
         api.default_config(1, 0, 1, 1)
 

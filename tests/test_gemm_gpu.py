@@ -42,6 +42,8 @@ def cfgs():
     out.append(C(block_n=256, cluster_m=2, epilogue=3))                # staged coalesced stores
     out.append(C(block_m=256, block_n=256, cluster_m=2, epilogue=3))
     out.append(C(block_n=192, cluster_m=1, epilogue=3))
+    for bm in (16, 32, 64):                                            # few-rows plan: operands swapped inside
+        out.append(C(block_m=bm, block_n=128, cluster_m=1))
     return out
 
 
@@ -459,3 +461,68 @@ def test_bounded_wait_gives_up_and_context_survives(g):
     a = util.integer_bits((256, 256), 1)
     b = util.integer_bits((256, 256), 2)
     assert np.array_equal(run(g, a, b), oracle.cpu_gemm(a, b))
+
+
+# ------------------------------------------------------------------------------------------------
+# Few-rows plan (block_m = 16 / 32 / 64): the caller's rows ride the MMA's N dimension, 128 rows
+# of B its M dimension, and the result is stored transposed. Default for M <= 64.
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("N,K", [(1024, 520), (1000, 77), (136, 8192), (4100, 1024)])
+def test_few_rows_default_integer_exact(g, M, N, K):
+    """cfg = NULL on decode-like shapes, tails in every dimension (N % 8 != 0, K % 8 != 0)."""
+    cfg = g.default_config(1, M, N, K)
+    assert cfg.block_m == (16 if M <= 16 else 32 if M <= 32 else 64) and cfg.sched == 2
+    a = util.integer_bits((M, K), 31 + M)
+    b = util.integer_bits((N, K), 32 + N)
+    ref = oracle.cpu_gemm(a, b)
+    assert np.array_equal(run(g, a, b), ref)
+    assert np.array_equal(run(g, a, b, alpha=0.5, beta=-2.0), oracle.cpu_gemm(a, b, 0.5, -2.0))
+
+
+@pytest.mark.parametrize("bm", [16, 32, 64])
+@pytest.mark.parametrize("sched,max_ctas", [(0, 0), (2, 0), (2, 7), (3, 5), (4, 5)])
+def test_few_rows_tiles_over_many_rows(g, bm, sched, max_ctas):
+    """block_m < 128 on a problem with many rows: tiles along both dimensions, every schedule."""
+    from h100_gemm_b200.api import GemmConfig as C
+    M, N, K = 200, 900, 3000
+    a = util.integer_bits((M, K), 41)
+    b = util.integer_bits((N, K), 42)
+    cfg = C(block_m=bm, block_n=128, cluster_m=1, sched=sched, max_ctas=max_ctas)
+    assert np.array_equal(run(g, a, b, cfg), oracle.cpu_gemm(a, b))
+
+
+def test_few_rows_general_inputs_and_column_major(g):
+    import torch
+    from h100_gemm_b200.api import GemmConfig as C
+    M, N, K = 48, 2048, 4096
+    a = util.normal_bits((M, K), 51)
+    b = util.normal_bits((N, K), 52, sigma=0.02)
+    ref = oracle.cpu_gemm(a, b)
+    assert_close(run(g, a, b), ref, a, b)
+    # column-major C together with the few-rows plan: the kernel's own orientation, stored as it is
+    out = g.gemm(util.to_device(a), util.to_device(b), out=torch.empty(N, M, dtype=torch.bfloat16, device="cuda"),
+                 cfg=C(block_m=64, block_n=128, cluster_m=1, c_col_major=1))
+    assert g.device_status()[0] == 0
+    assert_close(np.ascontiguousarray(util.to_bits(out).T), ref, a, b)
+    # split-K has no few-rows form
+    with pytest.raises(g.GemmError):
+        g.gemm(util.to_device(a), util.to_device(b), cfg=C(block_m=16, block_n=128, cluster_m=1, sched=1, split_k=2))
+
+
+def test_few_rows_fp16_and_batched(g):
+    import torch
+    from h100_gemm_b200.api import GemmConfig as C
+    gen = torch.Generator(device="cuda").manual_seed(61)
+    a = torch.randint(-4, 5, (24, 1032), device="cuda", generator=gen).to(torch.float16)
+    b = torch.randint(-4, 5, (776, 1032), device="cuda", generator=gen).to(torch.float16)
+    out = g.gemm(a, b)
+    assert g.default_config(1, 24, 776, 1032).block_m == 32
+    assert torch.equal(out.float(), a.float() @ b.float().t())
+    # batched: three problems, bf16
+    ab = torch.randint(-4, 5, (3, 40, 520), device="cuda", generator=gen).to(torch.bfloat16)
+    bb = torch.randint(-4, 5, (3, 300, 520), device="cuda", generator=gen).to(torch.bfloat16)
+    for cfg in (None, C(block_m=16, block_n=128, cluster_m=1, sched=2)):
+        ob = g.gemm_batched(ab, bb, cfg=cfg)
+        assert torch.equal(ob.float(), torch.bmm(ab.float(), bb.float().transpose(1, 2)))
+    assert g.device_status()[0] == 0

@@ -80,10 +80,20 @@ def test_tuner_end_to_end_two_configurations(tmp_path):
     best, runtime, results = tuner.tune()
     assert best is not None and 0 < runtime < 50 and all(r["success"] for r in results)
     # a configuration without a kernel is a failed run, not a crash of the tuner
-    bad = gt.GemmTuner(output_dir=str(tmp_path / "bad"), param_space=dict(space, BLOCKM=[64], CLUSTER_M=[1]),
+    bad = gt.GemmTuner(output_dir=str(tmp_path / "bad"), param_space=dict(space, BLOCKN=[96], CLUSTER_M=[1]),
                        shape=(512, 512, 512), timeout=120)
     best, _, results = bad.tune()
     assert best is None and not results[0]["success"]
+
+
+@pytest.mark.gpu
+def test_blockm_64_of_the_reference_space_runs(tmp_path):
+    """BLOCKM = 64, BLOCKN = 128 (gemm_tuner.py:17-24) maps to the few-rows plan: 64 x 128 tiles with
+    the operands swapped inside. The template's own check against the SIMT GEMM must pass."""
+    space = dict(CLUSTER_M=[1], CLUSTER_N=[1], BLOCKM=[64], BLOCKN=[128], BLOCKK=[64], STAGES=[5])
+    tuner = gt.GemmTuner(output_dir=str(tmp_path), param_space=space, shape=(1024, 1024, 512), timeout=120)
+    best, runtime, results = tuner.tune()
+    assert best is not None and results[0]["success"] and 0 < runtime < 50
 
 
 @pytest.mark.gpu

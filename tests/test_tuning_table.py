@@ -66,7 +66,7 @@ def test_stages_that_do_not_fit_a_neighbouring_shape_fall_back_to_as_many_as_fit
 
 def test_entries_without_a_kernel_are_refused():
     with pytest.raises(g.GemmError):
-        g.tuning_add(4096, 4096, 4096, g.GemmConfig(block_m=64, block_n=128, cluster_m=1))
+        g.tuning_add(4096, 4096, 4096, g.GemmConfig(block_m=96, block_n=128, cluster_m=1))
     with pytest.raises(g.GemmError):
         g.tuning_add(4096, 4096, 4096, g.GemmConfig(block_m=128, block_n=96, cluster_m=1))
     with pytest.raises(g.GemmError):
@@ -88,7 +88,7 @@ def test_load_file_roundtrip_and_errors(tmp_path):
         g.tuning_load(bad)
     assert g.tuning_size() == 4                      # nothing of a bad file is kept
     nokernel = tmp_path / "nokernel.table"
-    nokernel.write_text("1 1024 1024 1024 64 128 1 4 0 0 0 0 0\n")
+    nokernel.write_text("1 1024 1024 1024 96 128 1 4 0 0 0 0 0\n")
     with pytest.raises(g.GemmError):
         g.tuning_load(nokernel)
     with pytest.raises(g.GemmError):
