@@ -35,7 +35,11 @@ typedef enum b200_status {
 
 /* Tunable surface. The first six fields are the template variables of the reference's
  * matmul_h100.cu.jinja:9-14 / gemm_tuner.py:17-24 and keep their meaning:
- *   block_m   rows of C per CTA. 128 (one tcgen05 accumulator of 128 TMEM lanes).
+ *   block_m   rows of C per CTA: 128 (one tcgen05 accumulator of 128 TMEM lanes) or 256 (two of
+ *             them, sharing every B tile). 16, 32 or 64 select the few-rows plan for decode-like
+ *             shapes: a block_m x 128 tile computed with the operands swapped inside (128 rows of B
+ *             on the MMA's M dimension, block_m rows of A on its N dimension) and stored
+ *             transposed; it needs block_n = 128 (or 0), cluster_m = 1 and has no split-K form.
  *   block_n   columns of C per tile: 64, 128, 192 or 256.
  *   block_k   K-tile staged per pipeline stage: 64 (one 128-byte swizzle row).
  *   stages    shared-memory ring depth; 0 = as many as fit.
