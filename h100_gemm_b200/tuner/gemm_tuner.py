@@ -37,6 +37,16 @@ PKG = Path(__file__).resolve().parent.parent
 REPO = PKG.parent
 DEFAULT_TEMPLATE = PKG / "bench" / "matmul_b200.cu.jinja"
 
+# Decode-like shapes (M <= 64): the few-rows plan's tiles. Pass with --space few-rows.
+FEW_ROWS_PARAM_SPACE = {
+    'CLUSTER_M': [1],
+    'CLUSTER_N': [1],
+    'BLOCKM': [16, 32, 64],
+    'BLOCKN': [128],
+    'BLOCKK': [64],
+    'STAGES': [4, 6, 8, 9, 11, 12],
+}
+
 B200_PARAM_SPACE = {
     'CLUSTER_M': [1, 2],
     'CLUSTER_N': [1],
@@ -46,8 +56,9 @@ B200_PARAM_SPACE = {
     'STAGES': [3, 4, 6],
 }
 
-# The reference's space (gemm_tuner.py:17-24); BLOCKM 64/256 and STAGES beyond shared memory
-# have no kernel here and come back as failed configurations.
+# The reference's space (gemm_tuner.py:17-24). BLOCKM = 64 runs as the few-rows plan (64 x 128 tiles,
+# operands swapped inside) with CLUSTER_M = 1; larger clusters with it, and STAGES beyond shared
+# memory, have no kernel here and come back as failed configurations.
 REFERENCE_PARAM_SPACE = {
     'CLUSTER_M': [1, 2, 4, 8, 16],
     'CLUSTER_N': [1],
@@ -235,7 +246,7 @@ def main():
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     ap.add_argument("--template", default=str(DEFAULT_TEMPLATE))
     ap.add_argument("--output-dir", default="tuning_results")
-    ap.add_argument("--space", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--space", default="b200", choices=["b200", "reference", "few-rows"])
     ap.add_argument("--shape", type=int, nargs=3, action="append", metavar=("M", "N", "K"),
                     help="shape to tune (default 5120 5120 4096); may be repeated")
     ap.add_argument("--table", metavar="FILE", help="record each shape's best configuration in this tuning table")
@@ -243,7 +254,7 @@ def main():
     ap.add_argument("--compile-only", metavar="DIR")
     ap.add_argument("--run-only", metavar="DIR")
     args = ap.parse_args()
-    space = B200_PARAM_SPACE if args.space == "b200" else REFERENCE_PARAM_SPACE
+    space = {"b200": B200_PARAM_SPACE, "reference": REFERENCE_PARAM_SPACE, "few-rows": FEW_ROWS_PARAM_SPACE}[args.space]
     shapes = [tuple(sh) for sh in (args.shape or [[5120, 5120, 4096]])]
     if args.compile_only:
         tuner = GemmTuner(args.template, args.output_dir, space, shapes[0])
