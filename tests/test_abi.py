@@ -76,6 +76,7 @@ def test_default_config(lib):
     s = api.default_config(1, 16, 28672, 8192)
     assert (s.block_m, s.block_n, s.sched, s.cluster_m) == (16, 128, 2, 1) and s.stages == 12
     assert api.default_config(1, 33, 28672, 8192).block_m == 64
+    assert api.default_config(1, 16, 8192, 8192).sched == 0      # up to one wave of tiles: whole tiles
     # 65..128 rows keep 128-row tiles with a short A stage
     t = api.default_config(1, 100, 28672, 8192)
     assert (t.block_m, t.sched, t.cluster_m) == (128, 2, 1)
