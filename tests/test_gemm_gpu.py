@@ -528,3 +528,26 @@ def test_few_rows_fp16_and_batched(g):
         # integer-valued inputs: the fp32 sums are exact, so only the final rounding to bf16 remains
         assert torch.equal(ob, torch.bmm(ab.float(), bb.float().transpose(1, 2)).to(torch.bfloat16))
     assert g.device_status()[0] == 0
+
+
+def test_random_shapes_match_the_simt_gemm_bit_for_bit(g):
+    """Seeded random shapes around every dispatch boundary of cfg = NULL (few rows on either side,
+    one wave / several waves, N and K with and without 16-byte rows), integer-valued inputs: the
+    tcgen05 path and the plain SIMT GEMM (reference.h:49-90 semantics) must agree in every bit."""
+    import torch
+    rng = np.random.default_rng(2024)
+    gen = torch.Generator(device="cuda").manual_seed(2024)
+    shapes = []
+    for _ in range(36):
+        M = int(rng.choice([1, 3, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100, 128, 129, 200, 300]))
+        N = int(rng.choice([1, 7, 64, 127, 128, 129, 136, 1000, 1024, 2500, 19072]))
+        K = int(rng.choice([1, 8, 63, 64, 65, 520, 1000, 2048]))
+        shapes.append((M, N, K))
+    shapes += [(64, 19072, 264), (16, 40000, 72), (33, 129, 4097)]
+    for M, N, K in shapes:
+        a = torch.randint(-3, 4, (M, K), device="cuda", generator=gen).to(torch.bfloat16)
+        b = torch.randint(-3, 4, (N, K), device="cuda", generator=gen).to(torch.bfloat16)
+        got = g.gemm(a, b, alpha=0.5, beta=1.0)
+        want = g.reference_gpu_gemm(a, b, alpha=0.5, beta=1.0)
+        assert g.device_status()[0] == 0, (M, N, K)
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (M, N, K)
