@@ -42,9 +42,9 @@ WORKLOADS = {
 HBM_BOUND = {"skinny16", "skinny32", "skinny64", "skinny128"}
 
 # DRAM bytes (read + write) of one gemm_kernel launch, from the ncu captures summarised in
-# profiles/gemm_kernel_square8192.md (821.4 MB read + 120.2 MB written) and
+# profiles/gemm_kernel_square8192.md (821.1 MB read + 119.8 MB written) and
 # profiles/gemm_kernel_skinny16.md (472.4 MB + 4.9 MB); None where no capture exists.
-NCU_DRAM_BYTES_PER_LAUNCH = {"square8192": 9.416e8, "prefill_shard": 9.416e8, "skinny16": 4.773e8}
+NCU_DRAM_BYTES_PER_LAUNCH = {"square8192": 9.409e8, "prefill_shard": 9.409e8, "skinny16": 4.773e8}
 
 
 def measured_peaks():
