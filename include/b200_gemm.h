@@ -177,7 +177,8 @@ int b200_gemm_bf16_fixed_scratch(int M, int N, int K, const void* A, const void*
  * rank holds the whole C; no separate collective runs. The caller must order "all launches
  * complete" before anyone reads C (a barrier between the ranks, e.g. a one-element all-reduce on
  * the same stream). Needs N % 8 == 0 and 16-byte aligned copies. cfg == NULL picks the pair-tile
- * configuration the fused epilogue is built for; other tile shapes return
+ * configuration the fused epilogue is built for (256 rows per CTA for two or three ranks, 128 rows
+ * per CTA from four ranks on, as measured); other tile shapes return
  * B200_ERR_UNSUPPORTED_CFG. The reference has no multi-GPU path; this is the M-sharded
  * configuration with the collective that follows the kernel folded into it. */
 int b200_gemm_bf16_gather(int M, int N, int K, const void* A, const void* B, void* const* C_all, int world,
