@@ -39,7 +39,7 @@ class GemmError(RuntimeError):
 class _Cfg(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in (
         "block_m", "block_n", "block_k", "stages", "cluster_m", "cluster_n", "sched", "split_k",
-        "raster", "group", "c_col_major", "max_ctas", "epilogue")]
+        "raster", "group", "c_col_major", "max_ctas", "epilogue", "swap_ab")]
 
 
 @dataclass
@@ -58,11 +58,12 @@ class GemmConfig:
     c_col_major: int = 0
     max_ctas: int = 0
     epilogue: int = 0
+    swap_ab: int = 0
 
     def _c(self) -> _Cfg:
         return _Cfg(self.block_m, self.block_n, self.block_k, self.stages, self.cluster_m,
                     self.cluster_n, self.sched, self.split_k, self.raster, self.group,
-                    self.c_col_major, self.max_ctas, self.epilogue)
+                    self.c_col_major, self.max_ctas, self.epilogue, self.swap_ab)
 
 
 def library() -> ctypes.CDLL:

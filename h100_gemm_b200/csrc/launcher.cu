@@ -198,6 +198,10 @@ const KernelEntry* find_kernel(int bn, int pair, int mt) {
       make_entry<64, 0, 1>(),  make_entry<128, 0, 1>(), make_entry<192, 0, 1>(), make_entry<256, 0, 1>(),
       make_entry<64, 1, 1>(),  make_entry<128, 1, 1>(), make_entry<192, 1, 1>(), make_entry<256, 1, 1>(),
       make_entry<128, 0, 2>(), make_entry<256, 0, 2>(), make_entry<128, 1, 2>(), make_entry<256, 1, 2>(),
+      // narrow accumulators as CTA pairs and with two sub-tiles: the few-rows plan only
+      make_entry<16, 1, 1>(),  make_entry<32, 1, 1>(),
+      make_entry<16, 0, 2>(),  make_entry<32, 0, 2>(),  make_entry<64, 0, 2>(),
+      make_entry<16, 1, 2>(),  make_entry<32, 1, 2>(),  make_entry<64, 1, 2>(),
   };
   for (const auto& e : table)
     if (e.bn == bn && e.pair == pair && e.mt == mt) return &e;
@@ -352,7 +356,7 @@ struct Plan {
   int max_ctas;
   int c_col_major;
   int store_mode;  // StoreMode to use when C is 16-byte aligned
-  int few_rows;    // 1: block_m < 128 — the caller's rows ride the MMA's N (operands swapped inside)
+  int few_rows;    // 1: the caller's rows ride the MMA's N (operands swapped inside)
 };
 
 // Default configuration from the shape. For M > 128 the candidates are ranked by a small cost
@@ -436,14 +440,20 @@ int resolve_plan(const b200_gemm_cfg& c, Plan* p) {
   int cm = c.cluster_m == 0 ? 1 : c.cluster_m;
   if (cm < 1 || cm > 16 || (cm & (cm - 1)) != 0) return B200_ERR_UNSUPPORTED_CFG;
   p->few_rows = 0;
-  if (c.block_m == 16 || c.block_m == 32 || c.block_m == 64) {
-    // Few-rows plan: a block_m x 128 tile computed with the operands swapped — 128 rows of B on the
-    // MMA's M dimension, block_m rows of A on its N dimension — and stored transposed. Single CTA.
-    if ((c.block_n != 0 && c.block_n != 128) || cm != 1) return B200_ERR_UNSUPPORTED_CFG;
+  if (c.swap_ab != 0 || c.block_m == 16 || c.block_m == 32 || c.block_m == 64) {
+    // Few-rows plan: the operands are swapped inside — rows of B ride the MMA's M dimension (128 per
+    // sub-tile, block_n = 128 or 256 of them per CTA), block_m rows of A ride its N dimension — and
+    // the product is stored transposed. cluster_m = 2 runs a CTA pair: each CTA then stages only
+    // half of the block_m rows of A next to its own rows of B.
+    const int rows = c.block_m == 0 ? 128 : c.block_m;
+    if (rows != 16 && rows != 32 && rows != 64 && rows != 128) return B200_ERR_UNSUPPORTED_CFG;
+    const int b_rows = c.block_n == 0 ? 128 : c.block_n;
+    if (b_rows != 128 && b_rows != 256) return B200_ERR_UNSUPPORTED_CFG;
+    if (cm > 2) return B200_ERR_UNSUPPORTED_CFG;
     if (c.sched == kSplitK) return B200_ERR_UNSUPPORTED_CFG;  // the fix-up pass writes whole rows of C
     p->few_rows = 1;
-    p->pair = 0;
-    p->kernel = find_kernel(c.block_m, 0, 1);
+    p->pair = cm == 2 ? 1 : 0;
+    p->kernel = find_kernel(rows, p->pair, b_rows / 128);
   } else {
     if (c.block_m != 0 && c.block_m != 128 && c.block_m != 256) return B200_ERR_UNSUPPORTED_CFG;
     const int mt = c.block_m == 256 ? 2 : 1;
@@ -451,6 +461,7 @@ int resolve_plan(const b200_gemm_cfg& c, Plan* p) {
     if (bn < 64) return B200_ERR_UNSUPPORTED_CFG;  // the narrow kernels serve the few-rows plan only
     p->pair = cm >= 2 ? 1 : 0;
     p->kernel = find_kernel(bn, p->pair, mt);
+    if (p->kernel != nullptr && mt == 2 && bn < 128) p->kernel = nullptr;  // few-rows instantiations only
   }
   if (p->kernel == nullptr) return B200_ERR_UNSUPPORTED_CFG;
   if (c.stages < 0) return B200_ERR_INVALID_ARG;
@@ -552,7 +563,7 @@ void tuning_add_locked(const TunedEntry& n) {
 }
 
 // Text format, one entry per line, '#' starts a comment:
-//   batch M N K block_m block_n cluster_m stages sched split_k raster group epilogue
+//   batch M N K block_m block_n cluster_m stages sched split_k raster group epilogue [swap_ab]
 // Returns the number of entries added (>= 0), or -B200_ERR_* when the file cannot be opened, a
 // line is malformed or names a configuration without a kernel; then nothing is added.
 int tuning_load_file(const char* path) {
@@ -564,12 +575,12 @@ int tuning_load_file(const char* path) {
   while (status == B200_OK && std::fgets(line, sizeof line, f) != nullptr) {
     char* hash = std::strchr(line, '#');
     if (hash != nullptr) *hash = '\0';
-    int v[13];
+    int v[14] = {};
     char extra;
-    const int n = std::sscanf(line, "%d %d %d %d %d %d %d %d %d %d %d %d %d %c", &v[0], &v[1], &v[2], &v[3], &v[4],
-                              &v[5], &v[6], &v[7], &v[8], &v[9], &v[10], &v[11], &v[12], &extra);
+    const int n = std::sscanf(line, "%d %d %d %d %d %d %d %d %d %d %d %d %d %d %c", &v[0], &v[1], &v[2], &v[3], &v[4],
+                              &v[5], &v[6], &v[7], &v[8], &v[9], &v[10], &v[11], &v[12], &v[13], &extra);
     if (n <= 0) continue;  // blank line or comment
-    if (n != 13) {
+    if (n != 13 && n != 14) {  // the fourteenth column (swap_ab) is optional
       status = B200_ERR_INVALID_ARG;
       break;
     }
@@ -590,6 +601,7 @@ int tuning_load_file(const char* path) {
     e.cfg.raster = v[10];
     e.cfg.group = v[11];
     e.cfg.epilogue = v[12];
+    e.cfg.swap_ab = n == 14 ? v[13] : 0;
     status = tuning_validate(e.batch, e.M, e.N, e.K, e.cfg);
     if (status == B200_OK && read.size() >= kMaxTunedEntries) status = B200_ERR_INVALID_ARG;
     if (status == B200_OK) read.push_back(e);
@@ -1065,7 +1077,16 @@ int b200_run_kernel(int M, int N, int K, void* A, void* B, void* C, int* DB) {
     cfg = heuristic_cfg(1, M, N, K);  // few caller rows
   } else {
     cfg = default_cfg(1, N, M, K);
-    if (cfg.block_m < 128) cfg = heuristic_cfg(1, 128, M, K);  // few kernel rows (small N): short A tile
+    if (cfg.block_m < 128 || cfg.swap_ab) {
+      // few kernel rows (small N): one CTA per 128-column tile with a short A stage
+      std::memset(&cfg, 0, sizeof(cfg));
+      cfg.block_m = 128;
+      cfg.block_n = 128;
+      cfg.block_k = 64;
+      cfg.cluster_m = 1;
+      cfg.cluster_n = 1;
+      cfg.epilogue = 2;
+    }
   }
   cfg.sched = kDataParallel;
   cfg.c_col_major = 1;

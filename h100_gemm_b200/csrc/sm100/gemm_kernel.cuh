@@ -8,7 +8,8 @@
 //   warp 0      TMA producer   one lane streams A/B K-tiles into a shared-memory ring
 //   warp 1      MMA issuer     one lane issues tcgen05.mma; owns tensor-memory alloc/dealloc
 //   warps 2-5   epilogue       tcgen05.ld -> bf16 -> either swizzled smem -> TMA store, or
-//   (2-9 if MT = 2)            16-byte global stores straight from registers
+//   (4-11 if MT = 2; then      16-byte global stores straight from registers
+//    warps 2-3 idle)
 //
 // Barriers (all mbarriers in shared memory, every wait bounded):
 //   full[s]       TMA bytes of stage s have landed           (producer -> MMA issuer)
@@ -27,8 +28,9 @@
 // MT = 2 gives every CTA two 128-row sub-tiles of A per K-tile (a 256 x BN accumulator per CTA,
 // 512 x BN per pair): the B tile is then reused by twice as many MMAs per byte loaded, which cuts
 // L2 -> shared-memory traffic per FLOP by a quarter. With BN = 256 the two accumulators fill all
-// 512 tensor-memory columns, so there is one accumulator buffer and the epilogue of a tile is not
-// hidden behind the next tile's main loop.
+// 512 tensor-memory columns, so there is one accumulator buffer: what is exposed of a tile's
+// epilogue is the read-out of the accumulator (the epilogue warps drain it into registers and
+// hand it back before they store anything); the stores run under the next tile's main loop.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -100,7 +102,7 @@ struct GemmArgs {
   float alpha, beta;
   int scale;                  // 1: C = acc * alpha + beta (the scalar-beta rule of reference.h:40)
   int c_transposed;           // 1: element (row, col) of the kernel's product goes to C[col * ldc + row]
-                              //    (few-rows plan: the caller's rows ride the MMA's N; BN <= 64 kernels only)
+                              //    (few-rows plan: the caller's rows ride the MMA's N; 2-byte stores only)
   unsigned int* status;       // 4 words: code, block, tile, detail
 };
 
@@ -108,7 +110,6 @@ template <int BN, int PAIR, int MT>
 struct KernelTraits {
   static_assert(BN == 16 || BN == 32 || (BN % 64 == 0 && BN >= 64 && BN <= 256),
                 "BN must be 16, 32, 64, 128, 192 or 256");
-  static_assert(BN >= 64 || (PAIR == 0 && MT == 1), "narrow tiles are single-CTA, one sub-tile");
   static_assert(MT == 1 || MT == 2, "one or two 128-row sub-tiles of A per CTA");
   static constexpr int kCtaGroup = PAIR ? 2 : 1;
   static constexpr int kUmmaM = kCtaRows * kCtaGroup;         // rows of one tcgen05.mma
@@ -120,11 +121,26 @@ struct KernelTraits {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kChunks = MT * BN / kEpiChunkCols;     // 64-column chunks of a CTA's accumulator
   static constexpr int kEpiWarps = 4 * MT;                    // one per TMEM lane quadrant and sub-tile
-  static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  // First epilogue warp. With two sub-tiles the epilogue warps form warpgroups of their own (warps
+  // 4-11; warps 2 and 3 idle) so that the register file can be re-partitioned per warpgroup:
+  // 56 registers for the warpgroup of the two single-thread roles, 224 for the epilogue warps,
+  // which hold a whole 32 x 256 accumulator share packed to 16 bits while the buffer is handed back.
+  // The registers are re-divided inside what the CTA was launched with (384 threads x 168): a split
+  // that asks for more never gets it and the warps asking would wait for ever.
+  static constexpr int kEpiWarp0 = MT == 2 ? 4 : 2;
+  static constexpr int kThreads = 32 * (kEpiWarp0 + kEpiWarps);
+  static constexpr int kRoleRegs = 56;
+  static constexpr int kEpiRegs = 224;
+  static_assert(MT == 1 || 128 * kRoleRegs + 256 * kEpiRegs <= 384 * 168,
+                "register split exceeds the CTA's launch allocation");
   static constexpr int kSlabsPerWarp = 2 / MT;                // TMA-store staging slabs per warp
   static constexpr int kEpiBytes = kEpiWarps * kSlabsPerWarp * kEpiSlabBytes;  // 32 KB
   static constexpr int kAccCols = MT * BN;                    // TMEM columns of one accumulator buffer
   static constexpr int kAccStages = (2 * kAccCols <= 512) ? 2 : 1;
+  // One accumulator buffer of two sub-tiles: each sub-tile gets its own full/empty barrier pair, so
+  // sub-tile 0 is read out while the tile's last MMAs still run on sub-tile 1, and the next tile's
+  // first MMAs start on sub-tile 0 while sub-tile 1 is read out.
+  static constexpr bool kSplitAcc = (kAccStages == 1 && MT == 2);
   static constexpr int kTmemCols = (kAccStages * kAccCols <= 32)    ? 32
                                    : (kAccStages * kAccCols <= 64)  ? 64
                                    : (kAccStages * kAccCols <= 128) ? 128
@@ -262,9 +278,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       ptx::mbar_init(full_bar(s), 1);
       ptx::mbar_init(empty_bar(s), 1);
     }
-    for (int a = 0; a < kAccStages; ++a) {
+    for (int a = 0; a < (T::kSplitAcc ? 2 : kAccStages); ++a) {
       ptx::mbar_init(tmem_full_bar(a), 1);
-      ptx::mbar_init(tmem_empty_bar(a), T::kEpiWarps * G);
+      ptx::mbar_init(tmem_empty_bar(a), (T::kSplitAcc ? 4 : T::kEpiWarps) * G);
     }
     *abort_flag = 0u;
     ptx::fence_mbar_init();
@@ -287,6 +303,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   ptx::grid_dependency_wait();
 
   // ---------------------------------------------------------------- roles
+  if (warp < T::kEpiWarp0) {
+  if constexpr (MT == 2) ptx::setmaxnreg_dec<T::kRoleRegs>();
   if (warp == 0) {
     // ===== TMA producer =====
     if (lane == 0) {
@@ -357,13 +375,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       bool ok = true;
       long long wait_full = 0, wait_tmem = 0;
       while (ok && it.next(seg)) {
-        const long long tw0 = prof ? clock64() : 0;
-        if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u)) {
-          report_timeout(args, kStatusMmaTmemTimeout, seg.tile, acc, abort_flag);
-          break;
+        if constexpr (!T::kSplitAcc) {
+          const long long tw0 = prof ? clock64() : 0;
+          if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u)) {
+            report_timeout(args, kStatusMmaTmemTimeout, seg.tile, acc, abort_flag);
+            break;
+          }
+          if (prof) wait_tmem += clock64() - tw0;
+          ptx::tc_fence_after_sync();
         }
-        if (prof) wait_tmem += clock64() - tw0;
-        ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * T::kAccCols);
         for (int kt = seg.k_begin; kt < seg.k_end; ++kt) {
           const long long tw1 = prof ? clock64() : 0;
@@ -378,12 +398,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           for (int mt = 0; mt < MT; ++mt) {
             // sub-tile mt: rows [128*mt, 128*mt + 128) of this CTA's A tile -> columns [BN*mt, ...)
             const uint64_t desc_a = desc_a_cur + static_cast<uint64_t>(mt * ((kCtaRows * kBlockK * 2) >> 4));
+            if constexpr (T::kSplitAcc) {
+              if (kt == seg.k_begin) {  // the first MMA overwrites the sub-tile: it must have been read out
+                const long long tw0 = prof ? clock64() : 0;
+                if (!ptx::mbar_wait(tmem_empty_bar(mt), acc_phase ^ 1u)) {
+                  report_timeout(args, kStatusMmaTmemTimeout, seg.tile, mt, abort_flag);
+                  ok = false;
+                  break;
+                }
+                if (prof) wait_tmem += clock64() - tw0;
+                ptx::tc_fence_after_sync();
+              }
+            }
 #pragma unroll
             for (int k = 0; k < kBlockK / kUmmaK; ++k) {
               ptx::umma_f16<G>(tmem_d + mt * BN, desc_a + k * kDescKStep, desc_b_cur + k * kDescKStep,
                                idesc, (kt > seg.k_begin || k > 0) ? 1u : 0u);
             }
+            if constexpr (T::kSplitAcc) {
+              if (kt == seg.k_end - 1) {  // this sub-tile is complete once the MMAs issued so far are
+                if (PAIR) {
+                  ptx::umma_commit_pair(tmem_full_bar(mt), 3);
+                } else {
+                  ptx::umma_commit_1cta(tmem_full_bar(mt));
+                }
+              }
+            }
           }
+          if (!ok) break;
           if (PAIR) {
             ptx::umma_commit_pair(empty_cur, 3);
           } else {
@@ -403,10 +445,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
         }
         if (!ok) break;
-        if (PAIR) {
-          ptx::umma_commit_pair(tmem_full_bar(acc), 3);
-        } else {
-          ptx::umma_commit_1cta(tmem_full_bar(acc));
+        if constexpr (!T::kSplitAcc) {
+          if (PAIR) {
+            ptx::umma_commit_pair(tmem_full_bar(acc), 3);
+          } else {
+            ptx::umma_commit_1cta(tmem_full_bar(acc));
+          }
         }
         if (++acc == kAccStages) {
           acc = 0;
@@ -419,14 +463,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       }
     }
     __syncwarp();
+  }
   } else {
     // ===== epilogue warps =====
-    // Warp e = warp - 2 reads TMEM lane quadrant q = warp % 4 of sub-tile e / 4: rows q*32..q*32+31
+    if constexpr (MT == 2) ptx::setmaxnreg_inc<T::kEpiRegs>();
+    // Epilogue warp e reads TMEM lane quadrant q = warp % 4 of sub-tile e / 4: rows q*32..q*32+31
     // of that 128-row sub-tile, 64 columns at a time. The accumulator buffer is handed back to the
     // MMA issuer right after the warp's last TMEM read; conversion and stores of that last chunk
     // happen after the hand-back.
     constexpr int kChunksPerSub = BN / kEpiChunkCols;
-    const int e = warp - 2;
+    const int e = warp - T::kEpiWarp0;
     const int q = warp & 3;
     const int mt = e >> 2;
     // TMA mode: kSlabsPerWarp staging slabs per warp; staged-store mode: one transpose slab per warp
@@ -442,22 +488,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t store_count = 0;
-    const bool prof_epi = prof && warp == 2 && lane == 0;
+    const bool prof_epi = prof && warp == T::kEpiWarp0 && lane == 0;
     long long epi_wait = 0, epi_drain = 0, epi_busy = 0, epi_tiles = 0;
     while (it.next(seg)) {
       const long long te0 = prof_epi ? clock64() : 0;
-      if (!ptx::mbar_wait(tmem_full_bar(acc), acc_phase)) {
-        if (lane == 0) report_timeout(args, kStatusEpilogueTimeout, seg.tile, acc, abort_flag);
-        break;
-      }
-      ptx::tc_fence_after_sync();
-      const long long te1 = prof_epi ? clock64() : 0;
-      if (prof_epi) epi_wait += te1 - te0;
+      // Everything that does not need the accumulator is worked out before the wait for it: the
+      // divisions of tile_coord alone are several hundred cycles, and with a single accumulator
+      // buffer every cycle between "accumulator ready" and "buffer handed back" idles the tensor cores.
       const TileCoord tc = tile_coord(args.sched, seg.tile);
       const int cta_row0 = static_cast<int>(cta_rank) * T::kCtaM;  // this CTA's first row in the tile
       const int n_tile = tc.n * BN;
       const bool to_slot = seg.slot >= 0;
       const bool plain = !to_slot && !seg.finish;
+      const int acc_bar = T::kSplitAcc ? mt : acc;  // barrier pair of this warp's accumulator (sub-)buffer
+      if (!ptx::mbar_wait(tmem_full_bar(acc_bar), acc_phase)) {
+        if (lane == 0) report_timeout(args, kStatusEpilogueTimeout, seg.tile, acc_bar, abort_flag);
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const long long te1 = prof_epi ? clock64() : 0;
+      if (prof_epi) epi_wait += te1 - te0;
 
       // Stream-K finisher: wait for the other workers' partial tiles (added below, in K order).
       int contrib_first = 0, contrib_count = 0;
@@ -485,25 +535,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       if constexpr (BN < kEpiChunkCols) {
         // Narrow tile (16 or 32 columns): one tensor-memory read is the warp's whole share, so the
         // accumulator buffer goes back to the MMA issuer before anything is stored.
-        const int m_slab = tc.m * T::kBlockM + q * 32;     // this warp's first row (single CTA, MT = 1)
-        const int row_in_tile = q * 32 + static_cast<int>(lane);
+        const int tile_row = cta_row0 + mt * kCtaRows + q * 32;  // this warp's first row in the tile
+        const int m_slab = tc.m * T::kBlockM + tile_row;
+        const int row_in_tile = tile_row + static_cast<int>(lane);
         const int row = m_slab + static_cast<int>(lane);
         const bool row_live = row < args.M;
         const bool live = m_slab < args.M;                  // warp-uniform
         uint32_t v[BN];
         if (live) {
           ptx::tmem_ld_cols(tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                                static_cast<uint32_t>(acc * T::kAccCols),
+                                static_cast<uint32_t>(acc * T::kAccCols + mt * BN),
                             v);
           ptx::tmem_ld_wait();
         }
         ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive_cluster(tmem_empty_leader + 8u * static_cast<uint32_t>(acc));
+        if (lane == 0) ptx::mbar_arrive_cluster(tmem_empty_leader + 8u * static_cast<uint32_t>(acc_bar));
         if (prof_epi) epi_drain += clock64() - te1;
-        // fp32 partial tile of a narrow kernel: [4-column piece][row (128)][4 floats], so the 32
-        // lanes of a warp write 512 contiguous bytes per store instruction.
-        constexpr int kPieceStride = kCtaRows * 4;
+        // fp32 partial tile of a narrow kernel: [4-column piece][row of the tile][4 floats], so the
+        // 32 lanes of a warp write 512 contiguous bytes per store instruction.
+        constexpr int kPieceStride = T::kBlockM * 4;
         if (live && row_live) {
           if (to_slot) {
             float* dst = args.partial + static_cast<long long>(seg.slot) * (T::kBlockM * BN) + row_in_tile * 4;
@@ -555,6 +606,104 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
         }
       } else {
+      bool drained = false;
+      if constexpr (kAccStages == 1) {
+        // One accumulator buffer (the two sub-tiles fill tensor memory): the tensor cores idle until
+        // this buffer is handed back. So the warp first reads ALL of its share out — the first 64
+        // columns go straight into its staging slab, the rest is kept in registers packed to 16 bits —
+        // hands the buffer back, and only then issues the stores: the stores of tile i run under the
+        // main loop of tile i + 1. (Everything in registers would need more than the 168 a thread of
+        // a 320-thread CTA can have.)
+        if (plain && args.store_mode == kStoreTma) {
+          const int tile_row = cta_row0 + mt * kCtaRows + q * 32;
+          const int m_slab = tc.m * T::kBlockM + tile_row;
+          const bool rows_live = m_slab < args.M;  // warp-uniform
+          const uint32_t slab_first = slab0 + (store_count & (T::kSlabsPerWarp - 1)) * kEpiSlabBytes;
+          uint32_t packed[kChunksPerSub - 1][32];
+          if (rows_live) {
+            const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                    static_cast<uint32_t>(acc * T::kAccCols + mt * BN);
+            if (lane == 0) ptx::tma_store_wait_read<T::kSlabsPerWarp - 1>();  // the slab's last store has read it
+            __syncwarp();
+            // 32 columns per read, two register buffers: the read of piece i + 1 is in flight while
+            // piece i is converted. (Columns beyond N hold products of zero-filled rows of B: they
+            // are read like the others and never stored.)
+            constexpr int kPieces = 2 * kChunksPerSub;
+            uint32_t v[2][32];
+            ptx::tmem_ld_32x32b_x32(taddr0, v[0]);
+#pragma unroll
+            for (int i = 0; i < kPieces; ++i) {
+              const int c = i >> 1, h = i & 1;
+              ptx::tmem_ld_wait();
+              if (i + 1 < kPieces) ptx::tmem_ld_32x32b_x32(taddr0 + static_cast<uint32_t>((i + 1) * 32), v[(i + 1) & 1]);
+              uint32_t(&x)[32] = v[i & 1];
+              if (args.scale) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  x[j] = __float_as_uint(__fadd_rn(__fmul_rn(__uint_as_float(x[j]), args.alpha), args.beta));
+                }
+              }
+              if (c == 0) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  ptx::st_shared_v4(slab_first + sw128_offset(lane, static_cast<uint32_t>(h * 4 + j)),
+                                    pack16<F16>(__uint_as_float(x[8 * j + 0]), __uint_as_float(x[8 * j + 1])),
+                                    pack16<F16>(__uint_as_float(x[8 * j + 2]), __uint_as_float(x[8 * j + 3])),
+                                    pack16<F16>(__uint_as_float(x[8 * j + 4]), __uint_as_float(x[8 * j + 5])),
+                                    pack16<F16>(__uint_as_float(x[8 * j + 6]), __uint_as_float(x[8 * j + 7])));
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  packed[c - 1 < 0 ? 0 : c - 1][h * 16 + j] =
+                      pack16<F16>(__uint_as_float(x[2 * j]), __uint_as_float(x[2 * j + 1]));
+                }
+              }
+            }
+          }
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_cluster(tmem_empty_leader + 8u * static_cast<uint32_t>(acc_bar));
+          if (prof_epi) epi_drain += clock64() - te1;
+          if (rows_live) {
+#pragma unroll
+            for (int c = 0; c < kChunksPerSub; ++c) {
+              const int n0 = n_tile + c * kEpiChunkCols;
+              if (n0 < args.N) {
+                const uint32_t slab = slab0 + (store_count & (T::kSlabsPerWarp - 1)) * kEpiSlabBytes;
+                if (c > 0) {
+                  if (lane == 0) ptx::tma_store_wait_read<T::kSlabsPerWarp - 1>();
+                  __syncwarp();
+#pragma unroll
+                  for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      const uint32_t* w = &packed[c - 1 < 0 ? 0 : c - 1][h * 16 + 4 * j];
+                      ptx::st_shared_v4(slab + sw128_offset(lane, static_cast<uint32_t>(h * 4 + j)), w[0], w[1], w[2],
+                                        w[3]);
+                    }
+                  }
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                  if constexpr (NP > 1) {
+                    for (int p = 0; p < args.gather_world; ++p) {
+                      ptx::tma_store_3d(&maps_c.m[p], slab, n0, m_slab, tc.b);
+                    }
+                  } else {
+                    ptx::tma_store_3d(&maps_c.m[0], slab, n0, m_slab, tc.b);
+                  }
+                  ptx::tma_store_commit();
+                }
+                ++store_count;
+              }
+            }
+          }
+          drained = true;
+        }
+      }
+      if (!drained) {
 #pragma unroll 1
       for (int c = 0; c < kChunksPerSub; ++c) {  // 64-column chunks of this warp's sub-tile
         const int tile_row = cta_row0 + mt * kCtaRows + q * 32;  // this warp's first row in the tile
@@ -577,7 +726,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           ptx::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) {
-            ptx::mbar_arrive_cluster(tmem_empty_leader + 8u * static_cast<uint32_t>(acc));
+            ptx::mbar_arrive_cluster(tmem_empty_leader + 8u * static_cast<uint32_t>(acc_bar));
           }
           if (prof_epi) epi_drain += clock64() - te1;
         }
@@ -685,7 +834,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                   *reinterpret_cast<uint4*>(dst + h * 32 + j * 8) = w;
                 }
               }
-            } else if (BN <= kEpiChunkCols && args.c_transposed) {
+            } else if (args.c_transposed) {
               // few-rows plan: column j of the product is a row of the caller's C
               uint16_t* cbase = reinterpret_cast<uint16_t*>(args.C) + tc.b * args.c_batch_stride +
                                 (m_slab + static_cast<int>(lane));
@@ -746,6 +895,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         ++store_count;
       }
+      }  // chunk by chunk
       }  // wide tiles
       if (prof_epi) {
         epi_busy += clock64() - te1;

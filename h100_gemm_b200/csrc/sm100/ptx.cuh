@@ -62,6 +62,19 @@ B200_DEVICE uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
 B200_DEVICE void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 B200_DEVICE void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Re-partition the register file between the warpgroups of a CTA (all four warps of a warpgroup
+// execute the same instruction): the two single-thread roles give registers up, the epilogue
+// warpgroups take them. The reference does the same for its producer/consumer warpgroups
+// (matmul_h100.cu.jinja:889, matmul_utils.cuh:418,455).
+template <int R>
+B200_DEVICE void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(R));
+}
+template <int R>
+B200_DEVICE void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R));
+}
+
 B200_DEVICE void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }

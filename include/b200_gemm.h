@@ -39,7 +39,7 @@ typedef enum b200_status {
  *             them, sharing every B tile). 16, 32 or 64 select the few-rows plan for decode-like
  *             shapes: a block_m x 128 tile computed with the operands swapped inside (128 rows of B
  *             on the MMA's M dimension, block_m rows of A on its N dimension) and stored
- *             transposed; it needs block_n = 128 (or 0), cluster_m = 1 and has no split-K form.
+ *             transposed; see swap_ab below for its variants.
  *   block_n   columns of C per tile: 64, 128, 192 or 256.
  *   block_k   K-tile staged per pipeline stage: 64 (one 128-byte swizzle row).
  *   stages    shared-memory ring depth; 0 = as many as fit.
@@ -63,6 +63,10 @@ typedef enum b200_status {
  *             shared-memory slab per warp and written with coalesced 16-byte stores. C rows that are not 16-byte aligned
  *             are always written with 2-byte stores (the reference's epilogue,
  *             matmul_h100.cu.jinja:689-698).
+ *   swap_ab   1 selects the few-rows plan explicitly (block_m = 16, 32 or 64 imply it): block_m
+ *             (16, 32, 64 or 128) rows of A ride the MMA's N dimension; block_n (128 or 256) is the
+ *             number of rows of B each CTA puts on the MMA's M dimension per tile; cluster_m = 2 runs
+ *             a CTA pair in which each CTA stages only half of the block_m rows of A. No split-K.
  */
 typedef struct b200_gemm_cfg {
   int block_m;
@@ -78,6 +82,7 @@ typedef struct b200_gemm_cfg {
   int c_col_major;
   int max_ctas;
   int epilogue;
+  int swap_ab;
 } b200_gemm_cfg;
 
 /* Replaces gpu_gemm<AType,BType,CType,AccumType,CLUSTER_M,CLUSTER_N,BLOCKM,BLOCKN,BLOCKK,STAGES>
@@ -122,8 +127,8 @@ int b200_gemm_default_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg);
  * is looked up before the built-in heuristic: the exact shape if present, otherwise the entry of
  * the same class (batched or not; ceil(log2) of M, N and K) nearest in log2 distance.
  *   b200_gemm_tuning_load   reads a text file — one entry per line,
- *       batch M N K block_m block_n cluster_m stages sched split_k raster group epilogue
- *     ('#' starts a comment) — and returns the number of entries added, or -B200_ERR_* when the
+ *       batch M N K block_m block_n cluster_m stages sched split_k raster group epilogue [swap_ab]
+ *     ('#' starts a comment; the last column may be left out) — and returns the number of entries added, or -B200_ERR_* when the
  *     file cannot be read, a line is malformed or names a configuration without a kernel (then
  *     nothing is added). The environment variable B200_GEMM_TUNING_TABLE names a file that is
  *     loaded before the first lookup. h100_gemm_b200/tuner/gemm_tuner.py --table writes the format.

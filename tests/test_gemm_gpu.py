@@ -409,7 +409,9 @@ def test_error_codes(g):
     C = api.GemmConfig
     a = torch.zeros(256, 512, dtype=torch.bfloat16, device="cuda")
     b = torch.zeros(256, 512, dtype=torch.bfloat16, device="cuda")
-    for bad, status in ((C(block_n=100), api.STATUS_UNSUPPORTED_CFG), (C(block_m=64), api.STATUS_UNSUPPORTED_CFG),
+    for bad, status in ((C(block_n=100), api.STATUS_UNSUPPORTED_CFG), (C(block_m=48), api.STATUS_UNSUPPORTED_CFG),
+                        (C(block_m=64, block_n=192), api.STATUS_UNSUPPORTED_CFG),
+                        (C(block_m=128, block_n=512, swap_ab=1), api.STATUS_UNSUPPORTED_CFG),
                         (C(cluster_n=2), api.STATUS_UNSUPPORTED_CFG), (C(block_k=128), api.STATUS_UNSUPPORTED_CFG),
                         (C(block_n=256, cluster_m=1, stages=7), api.STATUS_SMEM), (C(sched=5), api.STATUS_INVALID_ARG)):
         with pytest.raises(api.GemmError) as e:
