@@ -500,16 +500,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const int n_tile = tc.n * BN;
       const bool to_slot = seg.slot >= 0;
       const bool plain = !to_slot && !seg.finish;
-      const int acc_bar = T::kSplitAcc ? mt : acc;  // barrier pair of this warp's accumulator (sub-)buffer
-      if (!ptx::mbar_wait(tmem_full_bar(acc_bar), acc_phase)) {
-        if (lane == 0) report_timeout(args, kStatusEpilogueTimeout, seg.tile, acc_bar, abort_flag);
-        break;
-      }
-      ptx::tc_fence_after_sync();
-      const long long te1 = prof_epi ? clock64() : 0;
-      if (prof_epi) epi_wait += te1 - te0;
-
-      // Stream-K finisher: wait for the other workers' partial tiles (added below, in K order).
+      // Stream-K finisher: wait for the other workers' partial tiles. They were written long ago
+      // (a contributor's partial is the first thing it computes), so for tiles of up to 128 columns
+      // this thread's share of their sum is fetched into registers NOW, while the tensor cores are
+      // still busy with this tile's K range: what remains after the accumulator is ready — the tail
+      // of the whole kernel for a decode shape — is one tensor-memory read, one add, the stores.
       int contrib_first = 0, contrib_count = 0;
       if (seg.finish) {
         contrib_count = streamk_contributors(args.sched, worker, seg.tile, &contrib_first);
@@ -531,6 +526,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           report_timeout(args, kStatusStreamKTimeout, seg.tile, contrib_first, abort_flag);
         }
       }
+      constexpr bool kPrefetchPartials = (BN < kEpiChunkCols) || (BN <= 64 && MT == 1);
+      float pre[kPrefetchPartials ? BN : 1];
+      if constexpr (kPrefetchPartials) {
+        const int row_in_tile = cta_row0 + mt * kCtaRows + q * 32 + static_cast<int>(lane);
+        if (contrib_count > 0 && tc.m * T::kBlockM + row_in_tile < args.M) {
+          for (int w = 0; w < contrib_count; ++w) {
+            const float* slot = args.partial + static_cast<long long>(contrib_first + w) * (T::kBlockM * BN);
+            if constexpr (BN < kEpiChunkCols) {
+              const float* src = slot + row_in_tile * 4;
+#pragma unroll
+              for (int j = 0; j < BN; j += 4) {
+                const float4 f = __ldcg(reinterpret_cast<const float4*>(src + (j / 4) * (T::kBlockM * 4)));
+                pre[j + 0] = w == 0 ? f.x : __fadd_rn(pre[j + 0], f.x);
+                pre[j + 1] = w == 0 ? f.y : __fadd_rn(pre[j + 1], f.y);
+                pre[j + 2] = w == 0 ? f.z : __fadd_rn(pre[j + 2], f.z);
+                pre[j + 3] = w == 0 ? f.w : __fadd_rn(pre[j + 3], f.w);
+              }
+            } else {
+#pragma unroll
+              for (int c = 0; c < BN / kEpiChunkCols; ++c) {
+                const float* src = slot + partial_fragment_offset<BN>(row_in_tile, c) + lane * 4;
+#pragma unroll
+                for (int k = 0; k < kEpiChunkCols; k += 4) {
+                  const float4 f = __ldcg(reinterpret_cast<const float4*>(src + (k / 4) * 128));
+                  float* d = &pre[c * kEpiChunkCols + k];
+                  d[0] = w == 0 ? f.x : __fadd_rn(d[0], f.x);
+                  d[1] = w == 0 ? f.y : __fadd_rn(d[1], f.y);
+                  d[2] = w == 0 ? f.z : __fadd_rn(d[2], f.z);
+                  d[3] = w == 0 ? f.w : __fadd_rn(d[3], f.w);
+                }
+              }
+            }
+          }
+        }
+      }
+      const int acc_bar = T::kSplitAcc ? mt : acc;  // barrier pair of this warp's accumulator (sub-)buffer
+      if (!ptx::mbar_wait(tmem_full_bar(acc_bar), acc_phase)) {
+        if (lane == 0) report_timeout(args, kStatusEpilogueTimeout, seg.tile, acc_bar, abort_flag);
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const long long te1 = prof_epi ? clock64() : 0;
+      if (prof_epi) epi_wait += te1 - te0;
 
       if constexpr (BN < kEpiChunkCols) {
         // Narrow tile (16 or 32 columns): one tensor-memory read is the warp's whole share, so the
@@ -565,17 +603,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                                  __uint_as_float(v[j + 3])));
             }
           } else {
-            for (int w = 0; w < contrib_count; ++w) {
-              const float* src =
-                  args.partial + static_cast<long long>(contrib_first + w) * (T::kBlockM * BN) + row_in_tile * 4;
+            if (contrib_count > 0) {  // (narrow tiles always have their contributors' sum in `pre`)
 #pragma unroll
-              for (int j = 0; j < BN; j += 4) {
-                const float4 f = __ldcg(reinterpret_cast<const float4*>(src + (j / 4) * kPieceStride));
-                v[j + 0] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 0]), f.x));
-                v[j + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 1]), f.y));
-                v[j + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 2]), f.z));
-                v[j + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 3]), f.w));
-              }
+              for (int j = 0; j < BN; ++j) v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), pre[j]));
             }
             if (args.scale) {
 #pragma unroll
@@ -752,7 +782,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
             continue;
           }
-          if (row_live) {
+          if constexpr (kPrefetchPartials) {
+            if (row_live && contrib_count > 0) {
+#pragma unroll
+              for (int cc = 0; cc < kChunksPerSub; ++cc) {  // (static register indexing: c is a run-time value)
+                if (cc == c) {
+#pragma unroll
+                  for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int k = 0; k < 32; ++k) {
+                      v[h][k] = __float_as_uint(
+                          __fadd_rn(__uint_as_float(v[h][k]), pre[(cc * kEpiChunkCols + h * 32 + k) % (kPrefetchPartials ? BN : 1)]));
+                    }
+                  }
+                }
+              }
+            }
+          } else if (row_live) {
             for (int j = 0; j < contrib_count; ++j) {
               const float* src = args.partial + static_cast<long long>(contrib_first + j) * (T::kBlockM * BN) +
                                  partial_fragment_offset<BN>(row_in_tile, c) + lane * 4;
