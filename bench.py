@@ -41,10 +41,11 @@ WORKLOADS = {
 }
 HBM_BOUND = {"skinny16", "skinny32", "skinny64", "skinny128"}
 
-# DRAM bytes (read + write) of one gemm_kernel launch, from the ncu captures summarised in
-# profiles/gemm_kernel_square8192.md (821.1 MB read + 119.8 MB written) and
-# profiles/gemm_kernel_skinny16.md (472.4 MB + 4.9 MB); None where no capture exists.
-NCU_DRAM_BYTES_PER_LAUNCH = {"square8192": 9.409e8, "prefill_shard": 9.409e8, "skinny16": 4.773e8}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one gemm_kernel launch, from ncu
+# captures of this benchmark's own command line on a B200; None where no capture exists.
+NCU_DRAM_BYTES_PER_LAUNCH = {"square8192": 9.409e8, "prefill_shard": 9.409e8, "skinny16": 4.773e8,
+                             "skinny64": 4.855e8, "skinny128": 4.982e8}
+INPUTS = {"uniform": "U[-1,1]", "normal": "N(0,1)", "normal0.02": "N(0,0.02)"}
 
 
 def measured_peaks():
@@ -228,7 +229,9 @@ def run_reference(args):
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{workload}: M={M} N={N} K={K} per GPU, C = A*B^T, bf16 in/out, fp32 accumulate",
-                   "l2": "CPU run"},
+                   "global_M": M * world, "parallelism": f"M-sharded x{world}, B replicated, no collective",
+                   "inputs": f"A ~ {INPUTS[ka]}, B ~ {INPUTS[kb]}",
+                   "l2": "inputs larger than L2 (no flush)" if not hbm else "3 rotating B buffers, each larger than L2"},
         "cpu_baseline": {"value": value, "unit": unit, "cores": used, "kind": kind,
                          "sample": f"each step: C[0:{a.shape[0]}, 0:{b.shape[0]}] of the problem (full K) with "
                                    f"reference_cpu_gemm (reference.h:5-46), {used} OpenMP threads"},
@@ -337,6 +340,87 @@ def run_sweep(args):
         torch.cuda.empty_cache()
 
 
+def bind_to_gpu_numa_node(index: int):
+    """Runs this process (and so its pinned host buffers, by first touch) on the CPUs the driver
+    reports as local to the GPU. Returns the number of CPUs bound to, or None if unknown."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        cpus &= set(os.sched_getaffinity(0))
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
+def skinny_leg(torch, g, device, stream, peaks, gpu_index, launches=50, sustained_s=0.6):
+    """The HBM-bound decode shapes (M in {16, 32, 64, 128}, N = 28672, K = 8192; A ~ N(0,1),
+    B ~ N(0,0.02)) on one GPU: a burst of `launches` back-to-back launches and a sustained run,
+    three rotating B buffers (each 470 MB, larger than L2), CUDA events on the launching stream,
+    clocks sampled during each region, cuBLAS on the same buffers beside it."""
+    import statistics
+    N, K = 28672, 8192
+    out = {}
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1)
+    bs = [(torch.randn((N, K), device=device, generator=gen) * 0.02).to(torch.bfloat16) for _ in range(3)]
+    try:
+        from h100_gemm_b200 import baselines
+    except Exception:
+        baselines = None
+    for M in (16, 32, 64, 128):
+        gen.manual_seed(100 + M)
+        a = torch.randn((M, K), device=device, generator=gen).to(torch.bfloat16)
+        c = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+        cfg = g.default_config(1, M, N, K)
+        ws = torch.empty(max(g.workspace_bytes(1, M, N, K, cfg), 1), dtype=torch.uint8, device=device)
+        nbytes = 2.0 * (M * K + N * K + M * N)
+
+        def ours(i):
+            g.gemm(a, bs[i % 3], out=c, cfg=cfg, workspace=ws, stream=stream)
+
+        def timed(fn, n):
+            for i in range(5):
+                fn(i)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with ClockSampler(gpu_index) as clk:
+                e0.record(stream)
+                for i in range(n):
+                    fn(i)
+                e1.record(stream)
+                torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n, clk.summary()
+
+        ms, clk = timed(ours, launches)
+        n_sus = max(launches, int(sustained_s * 1e3 / ms))
+        ms_sus, clk_sus = timed(ours, n_sus)
+        entry = {"M": M, "ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                 "launches": launches, "clocks": clk,
+                 "sustained": {"ms": ms_sus, "launches": n_sus, "gbs": nbytes / (ms_sus * 1e-3) / 1e9,
+                               "frac": nbytes / (ms_sus * 1e-3) / 1e9 / peaks["hbm_gbs"], "clocks": clk_sus},
+                 "algorithmic_bytes": int(nbytes),
+                 "kernel_cfg": {k: getattr(cfg, k) for k in ("block_m", "block_n", "stages", "cluster_m", "sched", "swap_ab")}}
+        if baselines is not None:
+            try:
+                v_ms, _ = timed(lambda i: baselines.cublas_gemm(a, bs[i % 3], out=c), launches)
+                entry["cublas_ms"] = v_ms
+                entry["ours_over_cublas_time"] = ms / v_ms
+            except Exception as exc:
+                entry["cublas_error"] = str(exc)[:200]
+        out[f"skinny{M}"] = entry
+    rc, words = g.device_status()
+    if rc != 0:
+        raise SystemExit(f"device status {words}")
+    return {"peak": peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth", "unit": "GB/s",
+            "l2": "3 rotating B buffers, each larger than L2", "shapes": out}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -350,8 +434,12 @@ def run_ours(args):
     g.library()
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    numa_cpus = bind_to_gpu_numa_node(physical_gpu_index(local))
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # The data path has no collective; the gather legs reported beside it run NCCL without the
+        # NVLink multicast path, so that a rank lost mid-run cannot fault its peers.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=device)
 
     workload = args.workload or ("square8192" if world == 1 else "prefill_shard")
@@ -459,7 +547,7 @@ def run_ours(args):
 
     # ---- optional: the same step followed by an NCCL all-gather of C, chunked and overlapped ----
     gathered = None
-    if world > 1 and args.allgather:
+    if world > 1 and not args.no_allgather:
         from h100_gemm_b200.sharding import ShardedGemm
         full = torch.empty(M * world, N, dtype=torch.bfloat16, device=device)
         comm_stream = torch.cuda.Stream(device=device)
@@ -522,9 +610,18 @@ def run_ours(args):
         except Exception as exc:
             gathered["fused"] = {"error": str(exc)[:300]}
 
+    # ---- N = 1: the HBM-bound decode shapes, reported beside the headline ----
+    skinny = None
+    if world == 1 and not args.kernel_only and not args.no_skinny and args.workload is None:
+        try:
+            skinny = skinny_leg(torch, g, device, stream, measured_peaks(), physical_gpu_index(local))
+        except RuntimeError as exc:  # this leg must never hide the headline result
+            skinny = {"error": str(exc)[:300]}
+        torch.cuda.empty_cache()
+
     # ---- end to end: pinned host buffers through the host-buffer C-ABI entry point ----
     e2e_steps = max(1, min(args.steps, 10))
-    e2e_s = float("nan")
+    e2e_s = copy_s = float("nan")
     if not args.kernel_only:
         ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
         hc = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
@@ -536,10 +633,18 @@ def run_ours(args):
             g.gemm_host(ha, hb, hc)
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
-    te = torch.tensor([e2e_s], dtype=torch.float64, device=device)
+        # the same copies without the kernels, all ranks at once: what the host links alone allow
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            g.gemm_host(ha, hb, hc, copies_only=True)
+        torch.cuda.synchronize()
+        copy_s = time.perf_counter() - t0
+        g.gemm_host(ha, hb, hc)  # leave the real result in hc
+    te = torch.tensor([e2e_s, copy_s], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_s = float(te.item())
+    e2e_s, copy_s = float(te[0].item()), float(te[1].item())
 
     flops_step = 2.0 * M * N * K
     bytes_step = 2.0 * (M * K + N * K + M * N)
@@ -570,11 +675,17 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": f"{workload}: M={M} N={N} K={K} per GPU, C = A*B^T, bf16 in/out, fp32 accumulate",
                        "global_M": M * world, "parallelism": f"M-sharded x{world}, B replicated, no collective",
-                       "l2": "inputs larger than L2 (no flush)" if not hbm else f"{rot} rotating B buffers, each larger than L2",
-                       "kernel_cfg": {k: getattr(cfg, k) for k in ("block_m", "block_n", "block_k", "stages", "cluster_m", "sched")}},
+                       "inputs": f"A ~ {INPUTS[ka]}, B ~ {INPUTS[kb]}",
+                       "l2": "inputs larger than L2 (no flush)" if not hbm else f"{rot} rotating B buffers, each larger than L2"},
+            "kernel_cfg": {k: getattr(cfg, k) for k in ("block_m", "block_n", "block_k", "stages", "cluster_m", "sched", "swap_ab")},
             "roofline": roof,
             "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int((M * K + N * K) * 2),
-                    "d2h_bytes_per_step": int(M * N * 2), "steps": e2e_steps},
+                    "d2h_bytes_per_step": int(M * N * 2), "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3,
+                    "bound": {"value": e2e_value * e2e_s / copy_s, "unit": unit, "ms_per_step": copy_s / e2e_steps * 1e3,
+                              "what": "the same host<->device copies without the kernels (b200_gemm_bf16_host_copies_only), "
+                                      "all ranks at once, max over ranks",
+                              "host_gbs_per_rank": (M * K + N * K + M * N) * 2 * e2e_steps / copy_s / 1e9},
+                    "frac_of_bound": copy_s / e2e_s, "cpus_bound_to": numa_cpus},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary(),
         }
@@ -589,6 +700,8 @@ def run_ours(args):
             sustained["peak"] = peak
             sustained["peak_source"] = f"{peaks['source']} " + ("copy bandwidth" if hbm else "cuBLAS bf16 sustained")
             line["sustained"] = sustained
+        if skinny is not None:
+            line["skinny"] = skinny
         if gathered is not None:
             line["with_allgather"] = gathered
         if vendor is not None:
@@ -613,8 +726,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
-    ap.add_argument("--allgather", action="store_true",
-                    help="N > 1: also time the variant that all-gathers C over NCCL (reported separately)")
+    ap.add_argument("--allgather", action="store_true", help="(kept for older command lines: the gather legs are on by default)")
+    ap.add_argument("--no-allgather", action="store_true",
+                    help="N > 1: skip the legs that also gather C on every rank (NCCL after the GEMM, and fused into "
+                         "the GEMM's epilogue); they are reported separately from the headline value")
+    ap.add_argument("--no-skinny", action="store_true", help="N = 1: skip the decode-shape (HBM-bound) leg")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for profiler captures)")
     ap.add_argument("--sweep", action="store_true",

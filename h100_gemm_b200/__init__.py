@@ -7,9 +7,9 @@ There is no CPU or library fallback: importing ``api`` without the built shared 
 calling it without a CUDA device, raises.
 """
 from .api import (GemmConfig, GemmError, default_config, device_status, gemm, gemm_batched,
-                  gemm_host, heuristic_config, library, reference_gpu_gemm, run_kernel, tuning_add,
+                  gemm_fixed_scratch, gemm_host, heuristic_config, library, reference_gpu_gemm, run_kernel, tuning_add,
                   tuning_clear, tuning_load, tuning_size, workspace_bytes)
 
 __all__ = ["GemmConfig", "GemmError", "default_config", "device_status", "gemm", "gemm_batched",
-           "gemm_host", "heuristic_config", "library", "reference_gpu_gemm", "run_kernel", "tuning_add",
+           "gemm_fixed_scratch", "gemm_host", "heuristic_config", "library", "reference_gpu_gemm", "run_kernel", "tuning_add",
            "tuning_clear", "tuning_load", "tuning_size", "workspace_bytes"]

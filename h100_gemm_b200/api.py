@@ -93,6 +93,8 @@ def library() -> ctypes.CDLL:
     lib.b200_run_kernel.restype = ci
     lib.b200_gemm_bf16_host.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf, cfgp]
     lib.b200_gemm_bf16_host.restype = ci
+    lib.b200_gemm_bf16_host_copies_only.argtypes = [ci, ci, ci, vp, vp, vp]
+    lib.b200_gemm_bf16_host_copies_only.restype = ci
     lib.b200_gemm_host_release.argtypes = []
     lib.b200_gemm_host_release.restype = None
     lib.b200_reference_gpu_gemm_bf16.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf, vp]
@@ -107,6 +109,8 @@ def library() -> ctypes.CDLL:
     if hasattr(lib, "b200_gemm_bf16_fixed_scratch"):
         lib.b200_gemm_bf16_fixed_scratch.argtypes = [ci, ci, ci, vp, vp, vp, cf, cf, vp]
         lib.b200_gemm_bf16_fixed_scratch.restype = ci
+        lib.b200_gemm_fixed_scratch_cfg.argtypes = [ci, ci, ci, cfgp]
+        lib.b200_gemm_fixed_scratch_cfg.restype = ci
     if hasattr(lib, "b200_gemm_bf16_gather"):
         lib.b200_gemm_bf16_gather.argtypes = [ci, ci, ci, vp, vp, ctypes.POINTER(vp), ci, ci, cfgp, vp]
         lib.b200_gemm_bf16_gather.restype = ci
@@ -128,6 +132,8 @@ def library() -> ctypes.CDLL:
     lib.b200_gemm_tuning_size.restype = ci
     lib.b200_gemm_heuristic_cfg.argtypes = [ci, ci, ci, ci, cfgp]
     lib.b200_gemm_heuristic_cfg.restype = ci
+    lib.b200_gemm_heuristic_cfg_for_sms.argtypes = [ci, ci, ci, ci, ci, cfgp]
+    lib.b200_gemm_heuristic_cfg_for_sms.restype = ci
     lib.b200_gemm_strerror.argtypes = [ci]
     lib.b200_gemm_strerror.restype = ctypes.c_char_p
     lib.b200_gemm_last_cuda_error.argtypes = []
@@ -185,6 +191,13 @@ def heuristic_config(batch: int, M: int, N: int, K: int) -> GemmConfig:
     """The built-in choice for a shape, ignoring the tuning table."""
     c = _Cfg()
     _check(library().b200_gemm_heuristic_cfg(batch, M, N, K, ctypes.byref(c)))
+    return GemmConfig(**{n: getattr(c, n) for n, _ in _Cfg._fields_})
+
+
+def heuristic_config_for_sms(batch: int, M: int, N: int, K: int, sm_count: int) -> GemmConfig:
+    """The built-in choice for a device with `sm_count` multiprocessors."""
+    c = _Cfg()
+    _check(library().b200_gemm_heuristic_cfg_for_sms(batch, M, N, K, sm_count, ctypes.byref(c)))
     return GemmConfig(**{n: getattr(c, n) for n, _ in _Cfg._fields_})
 
 
@@ -388,11 +401,13 @@ def reference_gpu_gemm(a, b, out=None, alpha: float = 1.0, beta: float = 0.0, st
 
 
 def gemm_host(a_bits, b_bits, out_bits=None, alpha: float = 1.0, beta: float = 0.0,
-              cfg: Optional[GemmConfig] = None):
+              cfg: Optional[GemmConfig] = None, copies_only: bool = False):
     """Host-buffer GEMM: numpy uint16 arrays holding bf16 bit patterns, [M,K] and [N,K].
 
     Copies to the device, multiplies and copies back inside the library (b200_gemm_bf16_host).
-    Accepts torch CPU tensors (pinned or not) of dtype bfloat16 as well.
+    Accepts torch CPU tensors (pinned or not) of dtype bfloat16 as well. ``copies_only`` runs the
+    same host<->device copies without the kernels (b200_gemm_bf16_host_copies_only): the time the
+    host links alone take, for benchmarks.
     """
     import numpy as np
 
@@ -415,7 +430,10 @@ def gemm_host(a_bits, b_bits, out_bits=None, alpha: float = 1.0, beta: float = 0
             out_bits = torch.empty((M, N), dtype=a_bits.dtype, pin_memory=a_bits.is_pinned())
     pc, _ = ptr_shape(out_bits)
     keep, p = _cfg_ptr(cfg)
-    _check(library().b200_gemm_bf16_host(M, N, K, pa, pb, pc, alpha, beta, p))
+    if copies_only:
+        _check(library().b200_gemm_bf16_host_copies_only(M, N, K, pa, pb, pc))
+    else:
+        _check(library().b200_gemm_bf16_host(M, N, K, pa, pb, pc, alpha, beta, p))
     return out_bits
 
 

@@ -12,6 +12,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 
 #include <atomic>
 #include <cmath>
@@ -21,6 +22,7 @@
 #include <cstring>
 #include <map>
 #include <random>
+#include <string>
 #include <mutex>
 #include <tuple>
 #include <vector>
@@ -363,7 +365,18 @@ struct Plan {
 // model: waves of tiles over the workers x tile area per SM x a penalty for the L2 -> shared
 // memory traffic each tile shape needs per FLOP (larger tiles move fewer bytes, which on a
 // power-limited part buys clock; smaller tiles fill the machine when there are few of them).
-b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K) {
+int heuristic_sm_count() {
+  int dev = 0, v = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) {
+    return v;
+  }
+  (void)cudaGetLastError();
+  return 148;  // a full B200, when there is no device to ask (sizing a workspace on a build machine)
+}
+
+b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K, int sms = 0) {
+  if (sms <= 0) sms = heuristic_sm_count();
   b200_gemm_cfg c;
   std::memset(&c, 0, sizeof(c));
   c.block_m = 128;
@@ -384,7 +397,7 @@ b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K) {
     // 16384: 28.2 / 46.4 us data-parallel against 29.6 / 48.6 us stream-K). Beyond one wave the
     // even split wins (N = 20480, 160 tiles: 58.2 us against 65.7 us).
     const long long tiles = static_cast<long long>((N + 127) / 128) * batch;
-    c.sched = tiles <= 148 ? kDataParallel : kStreamK;
+    c.sched = tiles <= sms ? kDataParallel : kStreamK;
     return c;
   }
   if (M <= 128) {
@@ -406,7 +419,6 @@ b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K) {
       {256, 256, 2, 1.00}, {256, 256, 1, 1.04}, {128, 256, 2, 1.05}, {256, 128, 1, 1.17},
       {128, 256, 1, 1.27}, {128, 128, 1, 1.58}, {128, 64, 1, 2.13},
   };
-  const int sms = 148;
   double best = 0.0;
   for (const Cand& k : cands) {
     const long long tile_m = static_cast<long long>(k.block_m) * k.cluster_m;
@@ -414,9 +426,10 @@ b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K) {
     const long long workers = sms / k.cluster_m;
     const long long waves = (tiles + workers - 1) / workers;
     double exposure = 1.0;
-    // A 256-row CTA tile has a single accumulator buffer, so its epilogue (a fixed number of
-    // cycles per tile) is exposed; the penalties above include it for K = 8192.
-    if (k.block_m == 256 && k.block_n == 256) exposure = 1.0 + 0.06 * (8192.0 / (K < 512 ? 512 : K) - 1.0);
+    // A 256-row CTA tile has a single accumulator buffer, so the read-out of the accumulator (a
+    // fixed number of cycles per tile, about 2 000 of 139 000 at K = 8192) is exposed; the penalties
+    // above include it for K = 8192.
+    if (k.block_m == 256 && k.block_n == 256) exposure = 1.0 + 0.02 * (8192.0 / (K < 512 ? 512 : K) - 1.0);
     const double area = static_cast<double>(k.block_m) * k.block_n * k.penalty * exposure;
     const double cost = static_cast<double>(waves) * area;
     // (The hybrid schedule — full waves data-parallel, last wave stream-K — is available as
@@ -614,13 +627,27 @@ int tuning_load_file(const char* path) {
   return static_cast<int>(read.size());
 }
 
+// The table loaded before the first lookup: the file B200_GEMM_TUNING_TABLE names, or — when the
+// variable is not set — the measured table shipped beside the library,
+// <directory of this shared object>/../tuner/b200_measured.table. Setting the variable to an empty
+// string starts with an empty table. Errors are ignored here (the table simply stays empty);
+// b200_gemm_tuning_load reports them.
+void tuning_load_default() {
+  const char* path = std::getenv("B200_GEMM_TUNING_TABLE");
+  if (path != nullptr) {
+    if (path[0] != '\0') (void)tuning_load_file(path);
+    return;
+  }
+  Dl_info info;
+  if (dladdr(reinterpret_cast<const void*>(&tuning_load_default), &info) == 0 || info.dli_fname == nullptr) return;
+  std::string lib(info.dli_fname);
+  const size_t slash = lib.rfind('/');
+  if (slash == std::string::npos) return;
+  (void)tuning_load_file((lib.substr(0, slash) + "/../tuner/b200_measured.table").c_str());
+}
+
 bool tuning_lookup(int batch, int M, int N, int K, b200_gemm_cfg* out) {
-  // B200_GEMM_TUNING_TABLE names a table file to load before the first lookup (errors: ignored
-  // here, the table simply stays empty; b200_gemm_tuning_load reports them).
-  std::call_once(g_tuned_env_once, [] {
-    const char* path = std::getenv("B200_GEMM_TUNING_TABLE");
-    if (path != nullptr && path[0] != '\0') (void)tuning_load_file(path);
-  });
+  std::call_once(g_tuned_env_once, tuning_load_default);
   std::lock_guard<std::mutex> lock(g_tuned_mutex);
   if (g_tuned.empty()) return false;
   const int cm = log2_ceil(M), cn = log2_ceil(N), ck = log2_ceil(K);
@@ -951,9 +978,11 @@ struct HostPath {
   size_t a_cap = 0, b_cap = 0, c_cap = 0, ws_cap = 0;
   cudaStream_t copy_in = nullptr, compute = nullptr, copy_out = nullptr;
   std::vector<cudaEvent_t> events;
-  int device = -1;
 };
-HostPath g_host;
+// One set of staging buffers, streams and events per device; calls are serialised by the mutex
+// (two host threads may use the entry point, one after the other).
+HostPath g_host[64];
+std::mutex g_host_mutex;
 
 int grow(void** p, size_t* cap, size_t need) {
   if (need <= *cap) return B200_OK;
@@ -1038,6 +1067,7 @@ int b200_gemm_default_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg) {
 // ------------------------------------------------------------------------------------------
 int b200_gemm_tuning_load(const char* path) {
   if (path == nullptr) return -B200_ERR_INVALID_ARG;
+  std::call_once(g_tuned_env_once, tuning_load_default);  // explicit entries go on top of the default table
   return tuning_load_file(path);
 }
 
@@ -1045,6 +1075,7 @@ int b200_gemm_tuning_add(int batch, int M, int N, int K, const b200_gemm_cfg* cf
   if (cfg == nullptr) return B200_ERR_INVALID_ARG;
   const int rc = tuning_validate(batch, M, N, K, *cfg);
   if (rc != B200_OK) return rc;
+  std::call_once(g_tuned_env_once, tuning_load_default);
   std::lock_guard<std::mutex> lock(g_tuned_mutex);
   if (g_tuned.size() >= kMaxTunedEntries) return B200_ERR_INVALID_ARG;
   tuning_add_locked(TunedEntry{batch, M, N, K, *cfg});
@@ -1052,11 +1083,13 @@ int b200_gemm_tuning_add(int batch, int M, int N, int K, const b200_gemm_cfg* cf
 }
 
 void b200_gemm_tuning_clear(void) {
+  std::call_once(g_tuned_env_once, [] {});  // a table cleared before its first use stays empty
   std::lock_guard<std::mutex> lock(g_tuned_mutex);
   g_tuned.clear();
 }
 
 int b200_gemm_tuning_size(void) {
+  std::call_once(g_tuned_env_once, tuning_load_default);
   std::lock_guard<std::mutex> lock(g_tuned_mutex);
   return static_cast<int>(g_tuned.size());
 }
@@ -1064,6 +1097,12 @@ int b200_gemm_tuning_size(void) {
 int b200_gemm_heuristic_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg) {
   if (cfg == nullptr || batch <= 0 || M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARG;
   *cfg = heuristic_cfg(batch, M, N, K);
+  return B200_OK;
+}
+
+int b200_gemm_heuristic_cfg_for_sms(int batch, int M, int N, int K, int sm_count, b200_gemm_cfg* cfg) {
+  if (cfg == nullptr || batch <= 0 || M <= 0 || N <= 0 || K <= 0 || sm_count <= 0) return B200_ERR_INVALID_ARG;
+  *cfg = heuristic_cfg(batch, M, N, K, sm_count);
   return B200_OK;
 }
 
@@ -1113,6 +1152,35 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 static void* g_static_scratch_ptr[64] = {};
 static std::mutex g_static_scratch_mutex;
 
+// The plan of the fixed-scratch entry point is pinned here, apart from the built-in heuristic and
+// the tuning table, because kStaticScratchBytes is sized for exactly these tiles: single-CTA
+// stream-K with 128-column tiles — 16/32/64 rows riding the MMA's N for M <= 64, a 128-row tile
+// with a short A stage above that.
+static b200_gemm_cfg fixed_scratch_cfg(int M, int N) {
+  b200_gemm_cfg c;
+  std::memset(&c, 0, sizeof(c));
+  c.block_k = 64;
+  c.cluster_m = 1;
+  c.cluster_n = 1;
+  c.group = 8;
+  c.block_n = 128;
+  c.sched = kStreamK;
+  if (M <= 64 && N >= 128) {
+    c.block_m = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  } else {
+    c.block_m = 128;
+    c.epilogue = 2;
+  }
+  return c;
+}
+
+int b200_gemm_fixed_scratch_cfg(int M, int N, int K, b200_gemm_cfg* cfg) {
+  if (cfg == nullptr || M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARG;
+  if (M > kCtaRows) return B200_ERR_STATIC_SCRATCH;
+  *cfg = fixed_scratch_cfg(M, N);
+  return B200_OK;
+}
+
 int b200_gemm_bf16_fixed_scratch(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
                                  float beta, void* stream) {
   int rc = validate(1, M, N, K, A, B, C);
@@ -1122,7 +1190,7 @@ int b200_gemm_bf16_fixed_scratch(int M, int N, int K, const void* A, const void*
   if (M > kCtaRows || K % 8 != 0 || (reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(B) & 15u)) {
     return B200_ERR_STATIC_SCRATCH;
   }
-  b200_gemm_cfg cfg = heuristic_cfg(1, M, N, K);  // never the tuning table: the scratch is sized for this plan
+  b200_gemm_cfg cfg = fixed_scratch_cfg(M, N);  // never the tuning table: the scratch is sized for this plan
   if (b200_gemm_workspace_bytes(1, M, N, K, &cfg) > kStaticScratchBytes) return B200_ERR_STATIC_SCRATCH;
 
   int dev = 0;
@@ -1241,18 +1309,18 @@ int b200_reference_gpu_gemm_f16(int M, int N, int K, const void* A, const void* 
   return B200_OK;
 }
 
-int b200_gemm_bf16_host(int M, int N, int K, const void* hA, const void* hB, void* hC, float alpha,
-                        float beta, const b200_gemm_cfg* cfg) {
+// The host-buffer call and its copy-only twin share one schedule: B whole, then row bands of A;
+// band i+1 is copied in while band i is multiplied and band i-1 is copied out.
+static int host_schedule(int M, int N, int K, const void* hA, const void* hB, void* hC, float alpha, float beta,
+                         const b200_gemm_cfg* cfg, bool launch) {
   int rc = validate(1, M, N, K, hA, hB, hC);
   if (rc != B200_OK) return rc;
   if (cfg != nullptr && cfg->c_col_major) return B200_ERR_UNSUPPORTED_CFG;
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
-  HostPath& h = g_host;
-  if (h.device != dev) {
-    b200_gemm_host_release();
-    h.device = dev;
-  }
+  if (dev < 0 || dev >= 64) return B200_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(g_host_mutex);
+  HostPath& h = g_host[dev];
   if (h.compute == nullptr) {
     B200_CUDA_TRY(cudaStreamCreateWithFlags(&h.copy_in, cudaStreamNonBlocking));
     B200_CUDA_TRY(cudaStreamCreateWithFlags(&h.compute, cudaStreamNonBlocking));
@@ -1265,16 +1333,16 @@ int b200_gemm_bf16_host(int M, int N, int K, const void* hA, const void* hB, voi
   if ((rc = grow(&h.dB, &h.b_cap, b_bytes)) != B200_OK) return rc;
   if ((rc = grow(&h.dC, &h.c_cap, c_bytes)) != B200_OK) return rc;
 
-  // Row bands of A (and C): band i+1 is copied in while band i is multiplied and band i-1 is
-  // copied out. Bands are multiples of 256 rows so every band tiles like the whole problem; a
-  // band must be worth a launch, hence at most 8 of them.
+  // Bands are multiples of 256 rows so every band tiles like the whole problem; a band must be
+  // worth a launch, hence at most 16 of them (the last band's GEMM and copy-out are the only part
+  // of the call that nothing overlaps).
   int bands = 1;
-  if (M >= 2048 && K % 8 == 0 && N % 8 == 0) bands = M >= 8192 ? 8 : 4;
+  if (M >= 2048 && K % 8 == 0 && N % 8 == 0) bands = M >= 8192 ? 16 : 4;
   const int band_rows = ((M + bands - 1) / bands + 255) / 256 * 256;
   bands = (M + band_rows - 1) / band_rows;
 
   size_t ws_need = 0;
-  for (int i = 0; i < bands; ++i) {
+  for (int i = 0; i < bands && launch; ++i) {
     const int rows = std::min(band_rows, M - i * band_rows);
     ws_need = std::max(ws_need, b200_gemm_workspace_bytes(1, rows, N, K, cfg));
   }
@@ -1285,42 +1353,67 @@ int b200_gemm_bf16_host(int M, int N, int K, const void* hA, const void* hB, voi
     h.events.push_back(e);
   }
 
-  B200_CUDA_TRY(cudaMemcpyAsync(h.dB, hB, b_bytes, cudaMemcpyHostToDevice, h.copy_in));
-  for (int i = 0; i < bands; ++i) {
+  // Once the first copy is enqueued the caller's buffers are in use by the device: every way out
+  // of the loop below, failures included, waits for the three streams first.
+  cudaError_t ce = cudaMemcpyAsync(h.dB, hB, b_bytes, cudaMemcpyHostToDevice, h.copy_in);
+  for (int i = 0; i < bands && ce == cudaSuccess && rc == B200_OK; ++i) {
     const int r0 = i * band_rows;
     const int rows = std::min(band_rows, M - r0);
     const size_t a_off = static_cast<size_t>(r0) * K * 2;
     const size_t c_off = static_cast<size_t>(r0) * N * 2;
-    B200_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(h.dA) + a_off,
-                                  static_cast<const uint8_t*>(hA) + a_off,
-                                  static_cast<size_t>(rows) * K * 2, cudaMemcpyHostToDevice, h.copy_in));
-    B200_CUDA_TRY(cudaEventRecord(h.events[2 * i], h.copy_in));
-    B200_CUDA_TRY(cudaStreamWaitEvent(h.compute, h.events[2 * i], 0));
-    rc = run_gemm(1, rows, N, K, static_cast<uint8_t*>(h.dA) + a_off, 0, h.dB, 0,
-                  static_cast<uint8_t*>(h.dC) + c_off, 0, alpha, beta, cfg, h.ws, h.ws_cap, h.compute);
-    if (rc != B200_OK) return rc;
-    B200_CUDA_TRY(cudaEventRecord(h.events[2 * i + 1], h.compute));
-    B200_CUDA_TRY(cudaStreamWaitEvent(h.copy_out, h.events[2 * i + 1], 0));
-    B200_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(hC) + c_off, static_cast<uint8_t*>(h.dC) + c_off,
-                                  static_cast<size_t>(rows) * N * 2, cudaMemcpyDeviceToHost, h.copy_out));
+    ce = cudaMemcpyAsync(static_cast<uint8_t*>(h.dA) + a_off, static_cast<const uint8_t*>(hA) + a_off,
+                         static_cast<size_t>(rows) * K * 2, cudaMemcpyHostToDevice, h.copy_in);
+    if (ce == cudaSuccess) ce = cudaEventRecord(h.events[2 * i], h.copy_in);
+    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(h.compute, h.events[2 * i], 0);
+    if (ce != cudaSuccess) break;
+    if (launch) {
+      rc = run_gemm(1, rows, N, K, static_cast<uint8_t*>(h.dA) + a_off, 0, h.dB, 0,
+                    static_cast<uint8_t*>(h.dC) + c_off, 0, alpha, beta, cfg, h.ws, h.ws_cap, h.compute);
+      if (rc != B200_OK) break;
+    }
+    ce = cudaEventRecord(h.events[2 * i + 1], h.compute);
+    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(h.copy_out, h.events[2 * i + 1], 0);
+    if (ce == cudaSuccess) {
+      ce = cudaMemcpyAsync(static_cast<uint8_t*>(hC) + c_off, static_cast<uint8_t*>(h.dC) + c_off,
+                           static_cast<size_t>(rows) * N * 2, cudaMemcpyDeviceToHost, h.copy_out);
+    }
   }
-  B200_CUDA_TRY(cudaStreamSynchronize(h.copy_out));
-  B200_CUDA_TRY(cudaStreamSynchronize(h.compute));
-  B200_CUDA_TRY(cudaStreamSynchronize(h.copy_in));
+  const cudaError_t s0 = cudaStreamSynchronize(h.copy_out);
+  const cudaError_t s1 = cudaStreamSynchronize(h.compute);
+  const cudaError_t s2 = cudaStreamSynchronize(h.copy_in);
+  if (rc != B200_OK) return rc;
+  for (cudaError_t e : {ce, s0, s1, s2}) B200_CUDA_TRY(e);
   return B200_OK;
 }
 
+int b200_gemm_bf16_host(int M, int N, int K, const void* hA, const void* hB, void* hC, float alpha,
+                        float beta, const b200_gemm_cfg* cfg) {
+  return host_schedule(M, N, K, hA, hB, hC, alpha, beta, cfg, /*launch=*/true);
+}
+
+int b200_gemm_bf16_host_copies_only(int M, int N, int K, const void* hA, const void* hB, void* hC) {
+  return host_schedule(M, N, K, hA, hB, hC, 1.0f, 0.0f, nullptr, /*launch=*/false);
+}
+
 void b200_gemm_host_release(void) {
-  HostPath& h = g_host;
-  if (h.dA) cudaFree(h.dA);
-  if (h.dB) cudaFree(h.dB);
-  if (h.dC) cudaFree(h.dC);
-  if (h.ws) cudaFree(h.ws);
-  for (cudaEvent_t e : h.events) cudaEventDestroy(e);
-  if (h.copy_in) cudaStreamDestroy(h.copy_in);
-  if (h.compute) cudaStreamDestroy(h.compute);
-  if (h.copy_out) cudaStreamDestroy(h.copy_out);
-  h = HostPath();
+  std::lock_guard<std::mutex> lock(g_host_mutex);
+  int current = 0;
+  const bool have_device = cudaGetDevice(&current) == cudaSuccess;
+  for (int dev = 0; dev < 64; ++dev) {
+    HostPath& h = g_host[dev];
+    if (h.compute == nullptr && h.dA == nullptr && h.dB == nullptr && h.dC == nullptr && h.ws == nullptr) continue;
+    if (cudaSetDevice(dev) != cudaSuccess) continue;
+    if (h.dA) cudaFree(h.dA);
+    if (h.dB) cudaFree(h.dB);
+    if (h.dC) cudaFree(h.dC);
+    if (h.ws) cudaFree(h.ws);
+    for (cudaEvent_t e : h.events) cudaEventDestroy(e);
+    if (h.copy_in) cudaStreamDestroy(h.copy_in);
+    if (h.compute) cudaStreamDestroy(h.compute);
+    if (h.copy_out) cudaStreamDestroy(h.copy_out);
+    h = HostPath();
+  }
+  if (have_device) cudaSetDevice(current);
   (void)cudaGetLastError();
 }
 

@@ -47,6 +47,10 @@ def max_over_ranks(value: float, device=None) -> float:
     return float(t.item())
 
 
+class GatherTimeout(RuntimeError):
+    """The exchange of C shards did not complete in time: a peer is gone or has fallen behind."""
+
+
 class ShardedGemm:
     """C[M,N] = A[M,K] @ B[N,K]^T with A and C row-sharded over the ranks of a process group.
 
@@ -77,9 +81,15 @@ class ShardedGemm:
         """No collective: every rank fills its own rows."""
         self.gemm_fn(self.a, self.b, out_shard)
 
-    def compute_and_gather(self, out_full, chunks: int = 4, comm_stream=None) -> None:
+    def compute_and_gather(self, out_full, chunks: int = 4, comm_stream=None, timeout_s: Optional[float] = None) -> None:
         """Fills the FULL C on every rank. Chunk j of every rank's shard is gathered while chunk
-        j+1 is being multiplied (side stream on CUDA; sequential under gloo)."""
+        j+1 is being multiplied (side stream on CUDA; sequential under gloo).
+
+        `timeout_s` bounds the host-side wait for the exchange: when a peer has left the job
+        between steps (it never posts its sends and receives), the call raises `GatherTimeout`
+        after at most that long instead of waiting for ever. (Under NCCL the exchange is
+        stream-ordered and the wait returns at once; there the process group's own timeout is the
+        bound.)"""
         import torch
         rows, N = self.rows, out_full.shape[1]
         pieces = chunk_rows(rows, chunks)
@@ -107,20 +117,39 @@ class ShardedGemm:
                     handles.extend(self.dist.batch_isend_irecv(ops))
             else:
                 handles.extend(self.dist.batch_isend_irecv(ops))
-        for h in handles:
-            h.wait()
+        if timeout_s is None:
+            for h in handles:
+                h.wait()
+        else:
+            import datetime
+            import time
+            deadline = time.monotonic() + timeout_s
+            for h in handles:
+                left = deadline - time.monotonic()
+                try:
+                    done = left > 0 and h.wait(datetime.timedelta(seconds=max(left, 1e-3)))
+                except RuntimeError as exc:  # gloo reports an expired wait as an error
+                    raise GatherTimeout(f"rank {self.rank}: gather did not complete within {timeout_s} s: {exc}") from exc
+                if done is False:
+                    raise GatherTimeout(f"rank {self.rank}: gather did not complete within {timeout_s} s")
         if use_cuda and comm_stream is not None:
             main.wait_stream(comm_stream)
 
 
 class FusedGatherGemm:
     """C = A @ B^T with A row-sharded over the ranks of one node and the all-gather of C done by
-    the GEMM kernel itself: every rank owns a full-C buffer that the other ranks map through CUDA
+    the GEMM kernel itself: every rank owns full-C buffers that the other ranks map through CUDA
     IPC, and each rank's epilogue stores its tiles into all of them over NVLink (TMA stores to
     peer memory; no multicast, no library collective on the data path).
 
-    Completion is ordered by a one-element all-reduce on the launching stream: it finishes on a
-    rank only after every rank has enqueued it behind its own GEMM launch.
+    Ordering. `run` enqueues, on ONE stream, the fused kernel and then a one-element all-reduce;
+    the all-reduce of step n completes on a rank only after every rank's kernel of step n has
+    completed, so work enqueued on that stream after `run` returns sees the whole C. Two full-C
+    buffers alternate between steps: the kernels of step n + 1 write into the other buffer, and
+    those of step n + 2 start only after the all-reduce of step n + 1, i.e. after every rank has
+    run — in stream order — everything it enqueued between its steps n and n + 1. So the readers
+    of a step's result must be enqueued on the same stream (or that stream must be made to wait
+    for them) before the next `run`; then no rank overwrites a buffer a peer still reads.
     """
 
     def __init__(self, M_shard: int, N: int, group=None):
@@ -133,20 +162,31 @@ class FusedGatherGemm:
         if self.world > 8:
             raise ValueError("the fused gather covers the ranks of one node (at most 8)")
         self.M, self.N = M_shard, N
-        nbytes = self.world * M_shard * N * 2
-        self.mine = api.DeviceBuffer(nbytes)
+        self.nbytes = self.world * M_shard * N * 2
+        self.mine = api.DeviceBuffer(2 * self.nbytes)
         handles = [None] * self.world
         dist.all_gather_object(handles, self.mine.handle(), group=group)
-        self.peers = [self.mine if p == self.rank else api.DeviceBuffer.from_handle(handles[p], nbytes)
+        self.peers = [self.mine if p == self.rank else api.DeviceBuffer.from_handle(handles[p], 2 * self.nbytes)
                       for p in range(self.world)]
-        self.ptrs = [b.ptr for b in self.peers]
-        self.full = self.mine.tensor((self.world * M_shard, N))
+        both = self.mine.tensor((2, self.world * M_shard, N))
+        self.buffers = [both[0], both[1]]
+        self.ptrs = [[b.ptr + half * self.nbytes for b in self.peers] for half in (0, 1)]
+        self.step = 0
+        self.full = self.buffers[0]  # the buffer the most recent run() filled
         self._token = torch.zeros(1, device="cuda")
 
-    def run(self, a_shard, b, cfg=None, stream=None) -> None:
-        """Enqueue the fused kernel and the completion barrier on the current stream."""
-        self.api.gemm_gather(a_shard, b, self.ptrs, self.rank, cfg=cfg, stream=stream)
-        self.dist.all_reduce(self._token, group=self.group)
+    def run(self, a_shard, b, cfg=None, stream=None):
+        """Enqueues the fused kernel and the completion all-reduce on `stream` (default: the
+        current stream) and returns this step's full C (also `self.full`)."""
+        torch = self.torch
+        stream = stream if stream is not None else torch.cuda.current_stream()
+        half = self.step & 1
+        with torch.cuda.stream(stream):
+            self.api.gemm_gather(a_shard, b, self.ptrs[half], self.rank, cfg=cfg, stream=stream)
+            self.dist.all_reduce(self._token, group=self.group)
+        self.full = self.buffers[half]
+        self.step += 1
+        return self.full
 
     def close(self) -> None:
         self.torch.cuda.synchronize()

@@ -37,15 +37,21 @@ PKG = Path(__file__).resolve().parent.parent
 REPO = PKG.parent
 DEFAULT_TEMPLATE = PKG / "bench" / "matmul_b200.cu.jinja"
 
-# Decode-like shapes (M <= 64): the few-rows plan's tiles. Pass with --space few-rows.
+# Decode-like shapes (M <= 128): the few-rows plan's tiles with whole tiles and with stream-K. Pass
+# with --space few-rows. SCHED and SWAP_AB are optional template variables (see OPTIONAL_KEYS).
 FEW_ROWS_PARAM_SPACE = {
     'CLUSTER_M': [1],
     'CLUSTER_N': [1],
-    'BLOCKM': [16, 32, 64],
+    'BLOCKM': [16, 32, 64, 128],
     'BLOCKN': [128],
     'BLOCKK': [64],
-    'STAGES': [4, 6, 8, 9, 11, 12],
+    'STAGES': [6, 8, 9, 11, 12],
+    'SCHED': [0, 2],
+    'SWAP_AB': [1],
 }
+
+# Template variables beyond the reference's six; a parameter dictionary may leave them out (= 0).
+OPTIONAL_KEYS = ('SCHED', 'SPLIT_K', 'RASTER', 'GROUP', 'EPILOGUE', 'SWAP_AB')
 
 B200_PARAM_SPACE = {
     'CLUSTER_M': [1, 2],
@@ -68,14 +74,15 @@ REFERENCE_PARAM_SPACE = {
     'STAGES': [3, 5, 7, 9, 11],
 }
 
-TABLE_HEADER = "# batch M N K block_m block_n cluster_m stages sched split_k raster group epilogue\n"
+TABLE_HEADER = "# batch M N K block_m block_n cluster_m stages sched split_k raster group epilogue swap_ab\n"
 
 
 def table_line(shape: Tuple[int, int, int], params: Dict[str, int], batch: int = 1) -> str:
-    """One tuning-table entry: the template's parameters for `shape`, data-parallel schedule."""
+    """One tuning-table entry: the template's parameters for `shape` (optional ones default to 0)."""
     m, n, k = shape
+    extra = ' '.join(str(params.get(key, 0)) for key in ('SCHED', 'SPLIT_K', 'RASTER', 'GROUP', 'EPILOGUE', 'SWAP_AB'))
     return (f"{batch} {m} {n} {k} {params['BLOCKM']} {params['BLOCKN']} {params['CLUSTER_M']} "
-            f"{params['STAGES']} 0 0 0 0 0")
+            f"{params['STAGES']} {extra}")
 
 
 def update_table(path, shape: Tuple[int, int, int], params: Dict[str, int], runtime_ms: Optional[float] = None,
@@ -101,7 +108,9 @@ LATENCY_RE = re.compile(r"Average latency \(ms\) is ([\d.]+)")
 
 
 def config_name(params: Dict[str, int]) -> str:
-    return "cm{CLUSTER_M}_cn{CLUSTER_N}_bm{BLOCKM}_bn{BLOCKN}_bk{BLOCKK}_st{STAGES}".format(**params)
+    name = "cm{CLUSTER_M}_cn{CLUSTER_N}_bm{BLOCKM}_bn{BLOCKN}_bk{BLOCKK}_st{STAGES}".format(**params)
+    tags = {'SCHED': 's', 'SPLIT_K': 'k', 'RASTER': 'r', 'GROUP': 'g', 'EPILOGUE': 'e', 'SWAP_AB': 'w'}
+    return name + ''.join(f"_{tags[key]}{params[key]}" for key in OPTIONAL_KEYS if params.get(key, 0))
 
 
 class GemmTuner:

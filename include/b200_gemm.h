@@ -130,18 +130,33 @@ int b200_gemm_default_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg);
  *       batch M N K block_m block_n cluster_m stages sched split_k raster group epilogue [swap_ab]
  *     ('#' starts a comment; the last column may be left out) — and returns the number of entries added, or -B200_ERR_* when the
  *     file cannot be read, a line is malformed or names a configuration without a kernel (then
- *     nothing is added). The environment variable B200_GEMM_TUNING_TABLE names a file that is
- *     loaded before the first lookup. h100_gemm_b200/tuner/gemm_tuner.py --table writes the format.
+ *     nothing is added). Before the first use of the table the library loads the file the
+ *     environment variable B200_GEMM_TUNING_TABLE names or, when the variable is not set, the
+ *     measured table shipped beside it (<directory of the shared object>/../tuner/
+ *     b200_measured.table); an empty value of the variable starts with an empty table.
+ *     h100_gemm_b200/tuner/gemm_tuner.py --table writes the format.
  *   b200_gemm_tuning_add    adds or replaces one entry (c_col_major and max_ctas must be 0: they
  *     are per-call choices).
  *   b200_gemm_tuning_clear / _size   empty the table / number of entries.
  *   b200_gemm_heuristic_cfg the built-in choice, ignoring the table.
- * b200_gemm_bf16_fixed_scratch and b200_gemm_bf16_gather never consult the table. */
+ * b200_gemm_bf16_fixed_scratch and b200_gemm_bf16_gather never consult the table.
+ *
+ * Stream-K and the hybrid schedules (sched 2, 3, 4 — the default for M <= 128 with many tiles)
+ * assume that the whole grid is resident at once: a worker that finishes a split tile waits, with a
+ * bound of about 0.1 s, for partial tiles of workers launched after it. The grid is sized for an
+ * otherwise idle device. When other kernels hold SMs at the same time (another stream of the same
+ * process, MPS), pass sched = 0 or cap the grid with max_ctas; a serving loop should also poll
+ * b200_gemm_last_device_status(), which reports a wait that gave up (the results of that launch are
+ * then not valid). */
 int b200_gemm_tuning_load(const char* path);
 int b200_gemm_tuning_add(int batch, int M, int N, int K, const b200_gemm_cfg* cfg);
 void b200_gemm_tuning_clear(void);
 int b200_gemm_tuning_size(void);
 int b200_gemm_heuristic_cfg(int batch, int M, int N, int K, b200_gemm_cfg* cfg);
+/* The same choice for a device with `sm_count` multiprocessors (the built-in heuristic counts waves
+ * of tiles over the SMs of the current device; 148 when there is none). No reference counterpart:
+ * its launcher hard-codes the SM count (matmul_h100_optimal.cu:40). */
+int b200_gemm_heuristic_cfg_for_sms(int batch, int M, int N, int K, int sm_count, b200_gemm_cfg* cfg);
 
 /* Replaces runKernel(int M,int N,int K,bf16* A,bf16* B,bf16* C,int* DB) —
  * matmul_h100_optimal.cu:32-59: default configuration, COLUMN-major C (ld = M), default stream.
@@ -155,15 +170,23 @@ int b200_run_kernel(int M, int N, int K, void* A, void* B, void* C, int* DB);
  * sequence (matmul_h100.cu.jinja:1036-1054). */
 int b200_gemm_bf16_host(int M, int N, int K, const void* hA, const void* hB, void* hC, float alpha,
                         float beta, const b200_gemm_cfg* cfg);
+/* The copies of b200_gemm_bf16_host without the kernels, in the same order on the same streams: what
+ * the host links alone allow for this shape (hC receives whatever the device buffer holds). A
+ * benchmark divides the two to see how much of the end-to-end time is the copies. State is kept
+ * per device; calls from several host threads are serialised; on any error the call returns only
+ * after its copies in flight have finished with the caller's buffers. */
+int b200_gemm_bf16_host_copies_only(int M, int N, int K, const void* hA, const void* hB, void* hC);
+/* Frees the staging buffers, streams and events of every device. */
 void b200_gemm_host_release(void);
 
 /* The few-rows GEMM (M <= 128, the decode shapes that run stream-K) for callers that cannot
  * allocate or pass device memory beyond the operands: a serving loop that fixes its device memory
  * plan at start-up and bans cudaMalloc afterwards, or a plug-in API with no workspace argument.
- * This entry point has no counterpart in the reference. It computes exactly what b200_gemm_bf16 does
- * with cfg == NULL, but keeps the stream-K partial tiles and flags in a 10 MiB array inside the
- * library image (so every GPU that loads the library holds that memory until exit) and calls no
- * cudaMalloc/cudaFree itself.
+ * This entry point has no counterpart in the reference. It computes what b200_gemm_bf16 does with
+ * the configuration b200_gemm_fixed_scratch_cfg returns (single-CTA stream-K tiles of 128 columns;
+ * never the tuning table, whatever it holds), but keeps the stream-K partial tiles and flags in a
+ * 10 MiB array inside the library image (so every GPU that loads the library holds that memory
+ * until exit) and calls no cudaMalloc/cudaFree itself.
  *   Limits: M <= 128, K % 8 == 0, A and B 16-byte aligned; anything else returns
  *     B200_ERR_STATIC_SCRATCH (use b200_gemm_bf16 with a workspace instead).
  *   First call on a device: looks up the array's device address (cudaGetSymbolAddress) and does
@@ -173,6 +196,9 @@ void b200_gemm_host_release(void);
  *     streams, or different host threads — race on it: serialise them on one stream. */
 int b200_gemm_bf16_fixed_scratch(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
                                  float beta, void* stream);
+/* The configuration b200_gemm_bf16_fixed_scratch runs for this shape (B200_ERR_STATIC_SCRATCH when
+ * M > 128); passing it to b200_gemm_bf16 with a workspace gives bit-identical results. */
+int b200_gemm_fixed_scratch_cfg(int M, int N, int K, b200_gemm_cfg* cfg);
 
 /* Row-sharded GEMM fused with the all-gather of C. Rank `rank` of `world` (<= 8) ranks on one node
  * holds M rows of A; C_all[p] is the base of rank p's copy of the FULL C ([world * M, N], bf16,

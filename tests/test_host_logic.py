@@ -84,7 +84,7 @@ CASES = [(4, 4, 1, 16), (32, 32, 1, 128), (1, 224, 1, 128), (3, 5, 2, 9), (1, 1,
 
 @pytest.mark.parametrize("tm,tn,batch,kt", CASES)
 @pytest.mark.parametrize("mode,split", [(0, 1), (1, 2), (1, 3), (1, 5), (2, 1), (3, 1), (4, 1)])
-@pytest.mark.parametrize("workers", [1, 7, 74, 148])
+@pytest.mark.parametrize("workers", [1, 7, 66, 74, 132, 148])
 def test_every_k_iteration_is_visited_exactly_once(shim, tm, tn, batch, kt, mode, split, workers):
     tiles = tm * tn * batch
     if mode == 1:

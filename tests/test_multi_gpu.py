@@ -31,18 +31,40 @@ def _worker(rank, world, port, q):
         b = (torch.randn(N, K, device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
         gen.manual_seed(100 + rank)                                     # this rank's rows of A
         a = torch.randn(M, K, device="cuda", generator=gen).to(torch.bfloat16)
+        import numpy as np
+        import util
+        from oracle import oracle  # the checker
         fg = FusedGatherGemm(M, N)
-        fg.run(a, b)
-        torch.cuda.synchronize()
-        mine = g.gemm(a, b)
-        own_ok = bool(torch.equal(fg.full[rank * M:(rank + 1) * M].view(torch.int16), mine.view(torch.int16)))
-        # what the other rank wrote into my copy must be what it computed for itself
-        parts = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(parts, mine)
-        full_ok = bool(torch.equal(fg.full.view(torch.int16), torch.cat(parts).view(torch.int16)))
+        own_ok = full_ok = oracle_ok = True
+        side = torch.cuda.Stream()
+        for step in range(4):
+            # a new A every step (the two full-C buffers alternate); steps 2 and 3 run on a side stream
+            a_step = (a * (step + 1)).to(torch.bfloat16)
+            stream = side if step >= 2 else None
+            if stream is not None:
+                stream.wait_stream(torch.cuda.current_stream())
+            full = fg.run(a_step, b, stream=stream)
+            if stream is not None:
+                torch.cuda.current_stream().wait_stream(stream)   # the readers below follow the all-reduce
+            mine = g.gemm(a_step, b)
+            own_ok &= bool(torch.equal(full[rank * M:(rank + 1) * M].view(torch.int16), mine.view(torch.int16)))
+            # what the other rank wrote into my copy must be what it computed for itself
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine)
+            full_ok &= bool(torch.equal(full.view(torch.int16), torch.cat(parts).view(torch.int16)))
+            if step == 0:
+                # and the peer's rows in MY copy equal the CPU oracle on the peer's inputs
+                peer = (rank + 1) % world
+                gen.manual_seed(100 + peer)
+                a_peer = torch.randn(M, K, device="cuda", generator=gen).to(torch.bfloat16)
+                rows = np.arange(0, M, 97, dtype=np.int32)
+                a_bits, b_bits = util.to_bits(a_peer), util.to_bits(b)
+                want = oracle.cpu_gemm_rows(a_bits, b_bits, rows)
+                got = util.to_bits(full[peer * M:(peer + 1) * M][rows.tolist()])
+                oracle_ok = oracle.norm_relative_error(got, want, a_bits[rows], b_bits) <= 1e-2
         status = g.device_status()[0]
         fg.close()
-        q.put((rank, own_ok, full_ok, status))
+        q.put((rank, own_ok, full_ok and oracle_ok, status))
     finally:
         dist.destroy_process_group()
 

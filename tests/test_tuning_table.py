@@ -112,6 +112,41 @@ def test_tuner_writes_what_the_library_reads(tmp_path):
     assert text.startswith("# batch M N K") and text.count("5120 5120 4096") == 1
 
 
+def test_shipped_table_is_loaded_when_no_environment_variable_is_set():
+    """cfg == NULL sees the measured entries without any set-up by the caller; an empty value of
+    the variable switches the default table off."""
+    entries = [line.split('#', 1)[0].split() for line in MEASURED.read_text().splitlines()]
+    entries = [[int(x) for x in e] for e in entries if e]
+    assert entries
+    code = ("import h100_gemm_b200 as g\n"
+            f"for e in {entries!r}:\n"
+            "    c = g.default_config(e[0], e[1], e[2], e[3])\n"
+            "    print(c.block_m, c.block_n, c.cluster_m, c.sched, c.epilogue, c.swap_ab, g.tuning_size())\n")
+    env = {k: v for k, v in os.environ.items() if k != "B200_GEMM_TUNING_TABLE"}
+    out = subprocess.run([sys.executable, "-c", code], cwd=REPO, env=env, capture_output=True, text=True, check=True)
+    rows = [[int(x) for x in line.split()] for line in out.stdout.splitlines()]
+    assert len(rows) == len(entries)
+    for e, r in zip(entries, rows):
+        swap = e[13] if len(e) > 13 else 0
+        assert r == [e[4], e[5], e[6], e[8], e[12], swap, len(entries)]
+    off = subprocess.run([sys.executable, "-c", "import h100_gemm_b200 as g; g.default_config(1, 2048, 2048, 2048); print(g.tuning_size())"],
+                         cwd=REPO, env=dict(env, B200_GEMM_TUNING_TABLE=""), capture_output=True, text=True, check=True)
+    assert off.stdout.split() == ["0"]
+
+
+def test_heuristic_counts_waves_over_the_sms_it_is_given():
+    from h100_gemm_b200 import api
+    # few rows, 140 tiles of 128 columns: one wave of whole tiles on 148 SMs, stream-K on 132
+    assert api.heuristic_config_for_sms(1, 16, 128 * 140, 4096, 148).sched == 0
+    assert api.heuristic_config_for_sms(1, 16, 128 * 140, 4096, 132).sched == 2
+    # 4096^3: 128 pair tiles of 512 x 256 are two waves on 74 pairs; with 128 pairs they are one,
+    # and so are the 256 tiles of 256 x 256 — the smaller tile then costs nothing extra
+    assert api.heuristic_config_for_sms(1, 4096, 4096, 4096, 148).block_m == 256
+    assert api.heuristic_config_for_sms(1, 4096, 4096, 4096, 512).block_m == 128
+    with pytest.raises(api.GemmError):
+        api.heuristic_config_for_sms(1, 16, 128, 128, 0)
+
+
 def test_environment_variable_loads_a_table_before_the_first_lookup():
     code = ("import h100_gemm_b200 as g; c = g.default_config(1, 2048, 2048, 2048); "
             "print(g.tuning_size(), c.block_m, c.block_n, c.cluster_m, c.stages)")
