@@ -365,6 +365,36 @@ struct Plan {
 // model: waves of tiles over the workers x tile area per SM x a penalty for the L2 -> shared
 // memory traffic each tile shape needs per FLOP (larger tiles move fewer bytes, which on a
 // power-limited part buys clock; smaller tiles fill the machine when there are few of them).
+// Cost model of the data-parallel tile shapes: waves of tiles over the workers x tile area x a
+// penalty for the L2 -> shared-memory traffic the shape needs per FLOP (time per unit of tile area
+// relative to the best shape, from tuner runs at 8192^3).
+struct TileCand {
+  int block_m, block_n, cluster_m;
+  double penalty;
+};
+const TileCand kTileCands[] = {
+    {256, 256, 2, 1.00}, {256, 256, 1, 1.04}, {128, 256, 2, 1.05}, {256, 128, 1, 1.17},
+    {128, 256, 1, 1.27}, {128, 128, 1, 1.58}, {128, 64, 1, 2.13},
+};
+
+double tile_cost(int block_m, int block_n, int cluster_m, int batch, int M, int N, int K, int sms) {
+  double penalty = 1.2;  // a shape the table above does not list
+  for (const TileCand& k : kTileCands) {
+    if (k.block_m == block_m && k.block_n == block_n && k.cluster_m == (cluster_m >= 2 ? 2 : 1)) penalty = k.penalty;
+  }
+  const int pair = cluster_m >= 2 ? 2 : 1;
+  const long long tile_m = static_cast<long long>(block_m) * pair;
+  const long long tiles = ((M + tile_m - 1) / tile_m) * ((N + block_n - 1) / block_n) * batch;
+  const long long workers = sms / pair;
+  const long long waves = (tiles + workers - 1) / workers;
+  double exposure = 1.0;
+  // A 256-row CTA tile has a single accumulator buffer, so the read-out of the accumulator (a
+  // fixed number of cycles per tile, about 2 000 of 139 000 at K = 8192) is exposed; the penalties
+  // above include it for K = 8192.
+  if (block_m == 256 && block_n == 256) exposure = 1.0 + 0.02 * (8192.0 / (K < 512 ? 512 : K) - 1.0);
+  return static_cast<double>(waves) * block_m * block_n * penalty * exposure;
+}
+
 int heuristic_sm_count() {
   int dev = 0, v = 0;
   if (cudaGetDevice(&dev) == cudaSuccess &&
@@ -411,37 +441,18 @@ b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K, int sms = 0) {
     c.epilogue = 2;
     return c;
   }
-  struct Cand {
-    int block_m, block_n, cluster_m;
-    double penalty;  // time per unit of tile area relative to the best shape (tuner, 8192^3)
-  };
-  static const Cand cands[] = {
-      {256, 256, 2, 1.00}, {256, 256, 1, 1.04}, {128, 256, 2, 1.05}, {256, 128, 1, 1.17},
-      {128, 256, 1, 1.27}, {128, 128, 1, 1.58}, {128, 64, 1, 2.13},
-  };
   double best = 0.0;
-  for (const Cand& k : cands) {
-    const long long tile_m = static_cast<long long>(k.block_m) * k.cluster_m;
-    const long long tiles = ((M + tile_m - 1) / tile_m) * ((N + k.block_n - 1) / k.block_n) * batch;
-    const long long workers = sms / k.cluster_m;
-    const long long waves = (tiles + workers - 1) / workers;
-    double exposure = 1.0;
-    // A 256-row CTA tile has a single accumulator buffer, so the read-out of the accumulator (a
-    // fixed number of cycles per tile, about 2 000 of 139 000 at K = 8192) is exposed; the penalties
-    // above include it for K = 8192.
-    if (k.block_m == 256 && k.block_n == 256) exposure = 1.0 + 0.02 * (8192.0 / (K < 512 ? 512 : K) - 1.0);
-    const double area = static_cast<double>(k.block_m) * k.block_n * k.penalty * exposure;
-    const double cost = static_cast<double>(waves) * area;
+  for (const TileCand& k : kTileCands) {
+    const double cost = tile_cost(k.block_m, k.block_n, k.cluster_m, batch, M, N, K, sms);
     // (The hybrid schedule — full waves data-parallel, last wave stream-K — is available as
     // sched = 3 but is not chosen here: measured on 3072^3..6144^3 it does not beat plain
     // data-parallel tiles, the partial-tile round trip costs about what the shorter wave saves.)
-    const int sched = kDataParallel;
     if (best == 0.0 || cost < best) {
       best = cost;
       c.block_m = k.block_m;
       c.block_n = k.block_n;
       c.cluster_m = k.cluster_m;
-      c.sched = sched;
+      c.sched = kDataParallel;
     }
   }
   return c;
@@ -669,7 +680,19 @@ bool tuning_lookup(int batch, int M, int N, int K, b200_gemm_cfg* out) {
     }
   }
   if (best == nullptr) return false;
-  *out = best->cfg;
+  // A neighbour's measured configuration carries over unless this shape quantises badly with it:
+  // for whole-tile schedules of many-row problems the cost model (waves x tile area) must not
+  // rate it more than a quarter above the heuristic's own choice. (1536^3 next to a 2048^3 entry
+  // of 128 x 256 tiles: 72 tiles on 148 SMs, where 128 x 128 tiles fill the machine.)
+  const b200_gemm_cfg& c = best->cfg;
+  if (M > 128 && c.sched == kDataParallel && !c.swap_ab && c.block_m >= 128) {
+    const int sms = heuristic_sm_count();
+    const b200_gemm_cfg h = heuristic_cfg(batch, M, N, K, sms);
+    const double mine = tile_cost(c.block_m, c.block_n ? c.block_n : 128, c.cluster_m, batch, M, N, K, sms);
+    const double theirs = tile_cost(h.block_m, h.block_n, h.cluster_m, batch, M, N, K, sms);
+    if (mine > 1.25 * theirs) return false;
+  }
+  *out = c;
   return true;
 }
 
@@ -1309,8 +1332,12 @@ int b200_reference_gpu_gemm_f16(int M, int N, int K, const void* A, const void* 
   return B200_OK;
 }
 
-// The host-buffer call and its copy-only twin share one schedule: B whole, then row bands of A;
-// band i+1 is copied in while band i is multiplied and band i-1 is copied out.
+// The host-buffer call and its copy-only twin share one schedule. A is cut into row bands and B
+// into row bands (column bands of C); the host -> device copies go A0, B0, B1, ..., then A1, A2, ...
+// and block C[i][j] is multiplied as soon as A_i and B_j are on the device and copied out right after,
+// so the first result leaves for the host after a quarter of B has arrived instead of all of it,
+// and what nothing overlaps at the end is one small block's kernel and copy. The host link towards
+// the device is the bottleneck of the whole call: everything else hides behind it.
 static int host_schedule(int M, int N, int K, const void* hA, const void* hB, void* hC, float alpha, float beta,
                          const b200_gemm_cfg* cfg, bool launch) {
   int rc = validate(1, M, N, K, hA, hB, hC);
@@ -1326,57 +1353,90 @@ static int host_schedule(int M, int N, int K, const void* hA, const void* hB, vo
     B200_CUDA_TRY(cudaStreamCreateWithFlags(&h.compute, cudaStreamNonBlocking));
     B200_CUDA_TRY(cudaStreamCreateWithFlags(&h.copy_out, cudaStreamNonBlocking));
   }
+
+  // Bands are multiples of 256 rows so every block tiles like a whole problem, and a block must be
+  // worth a launch: at most 8 bands of A and 4 of B.
+  const bool aligned = K % 8 == 0 && N % 8 == 0;
+  int na = 1, nb = 1;
+  if (aligned && M >= 2048) na = M >= 8192 ? 8 : 4;
+  if (aligned && N >= 4096) nb = 4;
+  const int a_rows = ((M + na - 1) / na + 255) / 256 * 256;
+  const int b_rows = ((N + nb - 1) / nb + 255) / 256 * 256;
+  na = (M + a_rows - 1) / a_rows;
+  nb = (N + b_rows - 1) / b_rows;
+
   const size_t a_bytes = static_cast<size_t>(M) * K * 2;
   const size_t b_bytes = static_cast<size_t>(N) * K * 2;
-  const size_t c_bytes = static_cast<size_t>(M) * N * 2;
+  // C blocks are stored compactly on the device, block (i, j) at slot i * nb + j
+  const size_t block_elems = static_cast<size_t>(a_rows) * b_rows;
+  const size_t c_bytes = block_elems * na * nb * 2;
   if ((rc = grow(&h.dA, &h.a_cap, a_bytes)) != B200_OK) return rc;
   if ((rc = grow(&h.dB, &h.b_cap, b_bytes)) != B200_OK) return rc;
   if ((rc = grow(&h.dC, &h.c_cap, c_bytes)) != B200_OK) return rc;
-
-  // Bands are multiples of 256 rows so every band tiles like the whole problem; a band must be
-  // worth a launch, hence at most 16 of them (the last band's GEMM and copy-out are the only part
-  // of the call that nothing overlaps).
-  int bands = 1;
-  if (M >= 2048 && K % 8 == 0 && N % 8 == 0) bands = M >= 8192 ? 16 : 4;
-  const int band_rows = ((M + bands - 1) / bands + 255) / 256 * 256;
-  bands = (M + band_rows - 1) / band_rows;
-
   size_t ws_need = 0;
-  for (int i = 0; i < bands && launch; ++i) {
-    const int rows = std::min(band_rows, M - i * band_rows);
-    ws_need = std::max(ws_need, b200_gemm_workspace_bytes(1, rows, N, K, cfg));
+  for (int i = 0; i < na && launch; ++i) {
+    for (int j = 0; j < nb; ++j) {
+      ws_need = std::max(ws_need, b200_gemm_workspace_bytes(1, std::min(a_rows, M - i * a_rows),
+                                                            std::min(b_rows, N - j * b_rows), K, cfg));
+    }
   }
   if ((rc = grow(&h.ws, &h.ws_cap, ws_need)) != B200_OK) return rc;
-  while (static_cast<int>(h.events.size()) < 2 * bands + 1) {
+  while (static_cast<int>(h.events.size()) < na + nb + na * nb) {
     cudaEvent_t e;
     B200_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     h.events.push_back(e);
   }
+  cudaEvent_t* ev_a = h.events.data();           // A_i on the device
+  cudaEvent_t* ev_b = ev_a + na;                 // B_j on the device
+  cudaEvent_t* ev_c = ev_b + nb;                 // C block computed
 
   // Once the first copy is enqueued the caller's buffers are in use by the device: every way out
-  // of the loop below, failures included, waits for the three streams first.
-  cudaError_t ce = cudaMemcpyAsync(h.dB, hB, b_bytes, cudaMemcpyHostToDevice, h.copy_in);
-  for (int i = 0; i < bands && ce == cudaSuccess && rc == B200_OK; ++i) {
-    const int r0 = i * band_rows;
-    const int rows = std::min(band_rows, M - r0);
-    const size_t a_off = static_cast<size_t>(r0) * K * 2;
-    const size_t c_off = static_cast<size_t>(r0) * N * 2;
-    ce = cudaMemcpyAsync(static_cast<uint8_t*>(h.dA) + a_off, static_cast<const uint8_t*>(hA) + a_off,
-                         static_cast<size_t>(rows) * K * 2, cudaMemcpyHostToDevice, h.copy_in);
-    if (ce == cudaSuccess) ce = cudaEventRecord(h.events[2 * i], h.copy_in);
-    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(h.compute, h.events[2 * i], 0);
-    if (ce != cudaSuccess) break;
+  // of the code below, failures included, waits for the three streams first.
+  cudaError_t ce = cudaSuccess;
+  auto copy_a = [&](int i) {
+    const size_t off = static_cast<size_t>(i) * a_rows * K * 2;
+    const size_t bytes = static_cast<size_t>(std::min(a_rows, M - i * a_rows)) * K * 2;
+    ce = cudaMemcpyAsync(static_cast<uint8_t*>(h.dA) + off, static_cast<const uint8_t*>(hA) + off, bytes,
+                         cudaMemcpyHostToDevice, h.copy_in);
+    if (ce == cudaSuccess) ce = cudaEventRecord(ev_a[i], h.copy_in);
+  };
+  auto copy_b = [&](int j) {
+    const size_t off = static_cast<size_t>(j) * b_rows * K * 2;
+    const size_t bytes = static_cast<size_t>(std::min(b_rows, N - j * b_rows)) * K * 2;
+    ce = cudaMemcpyAsync(static_cast<uint8_t*>(h.dB) + off, static_cast<const uint8_t*>(hB) + off, bytes,
+                         cudaMemcpyHostToDevice, h.copy_in);
+    if (ce == cudaSuccess) ce = cudaEventRecord(ev_b[j], h.copy_in);
+  };
+  auto block = [&](int i, int j) {  // multiply C[i][j] and send it to the host
+    const int rows = std::min(a_rows, M - i * a_rows), cols = std::min(b_rows, N - j * b_rows);
+    uint8_t* dc = static_cast<uint8_t*>(h.dC) + (static_cast<size_t>(i) * nb + j) * block_elems * 2;
+    // the copy stream is in order: of the two operands, the one copied later is the one to wait for
+    ce = cudaStreamWaitEvent(h.compute, i == 0 ? ev_b[j] : ev_a[i], 0);
+    if (ce != cudaSuccess) return;
     if (launch) {
-      rc = run_gemm(1, rows, N, K, static_cast<uint8_t*>(h.dA) + a_off, 0, h.dB, 0,
-                    static_cast<uint8_t*>(h.dC) + c_off, 0, alpha, beta, cfg, h.ws, h.ws_cap, h.compute);
-      if (rc != B200_OK) break;
+      rc = run_gemm(1, rows, cols, K, static_cast<uint8_t*>(h.dA) + static_cast<size_t>(i) * a_rows * K * 2, 0,
+                    static_cast<uint8_t*>(h.dB) + static_cast<size_t>(j) * b_rows * K * 2, 0, dc, 0, alpha, beta, cfg,
+                    h.ws, h.ws_cap, h.compute);
+      if (rc != B200_OK) return;
     }
-    ce = cudaEventRecord(h.events[2 * i + 1], h.compute);
-    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(h.copy_out, h.events[2 * i + 1], 0);
+    ce = cudaEventRecord(ev_c[i * nb + j], h.compute);
+    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(h.copy_out, ev_c[i * nb + j], 0);
     if (ce == cudaSuccess) {
-      ce = cudaMemcpyAsync(static_cast<uint8_t*>(hC) + c_off, static_cast<uint8_t*>(h.dC) + c_off,
-                           static_cast<size_t>(rows) * N * 2, cudaMemcpyDeviceToHost, h.copy_out);
+      ce = cudaMemcpy2DAsync(static_cast<uint8_t*>(hC) + (static_cast<size_t>(i) * a_rows * N + static_cast<size_t>(j) * b_rows) * 2,
+                             static_cast<size_t>(N) * 2, dc, static_cast<size_t>(cols) * 2, static_cast<size_t>(cols) * 2,
+                             static_cast<size_t>(rows), cudaMemcpyDeviceToHost, h.copy_out);
     }
+  };
+  auto ok = [&]() { return ce == cudaSuccess && rc == B200_OK; };
+
+  copy_a(0);
+  for (int j = 0; j < nb && ok(); ++j) {
+    copy_b(j);
+    if (ok()) block(0, j);
+  }
+  for (int i = 1; i < na && ok(); ++i) {
+    copy_a(i);
+    for (int j = 0; j < nb && ok(); ++j) block(i, j);
   }
   const cudaError_t s0 = cudaStreamSynchronize(h.copy_out);
   const cudaError_t s1 = cudaStreamSynchronize(h.compute);

@@ -163,8 +163,9 @@ int b200_gemm_heuristic_cfg_for_sms(int batch, int M, int N, int K, int sm_count
  * DB is accepted and ignored, as in the reference (matmul_h100_optimal.cu:32,58). */
 int b200_run_kernel(int M, int N, int K, void* A, void* B, void* C, int* DB);
 
-/* Same GEMM with HOST buffers (pageable or pinned): copies A and B to the device in row bands,
- * overlapping the copies with the kernel, and copies C back. Synchronous. It keeps device
+/* Same GEMM with HOST buffers (pageable or pinned): copies A and B to the device in row bands, runs
+ * one kernel per block of C as soon as its two bands have arrived and copies that block back, so
+ * that kernels and device -> host copies hide behind the host -> device copies. Synchronous. It keeps device
  * staging buffers between calls (released by b200_gemm_host_release). This is the call a
  * harness like the reference's main() makes around its copy_to_gpu / gpu_gemm / copy_to_cpu
  * sequence (matmul_h100.cu.jinja:1036-1054). */

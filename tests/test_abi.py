@@ -74,7 +74,9 @@ def test_default_config(lib):
     assert c.stages >= 3
     # decode shape: the 16 rows ride the MMA's N (16 x 128 tiles), K split evenly over the SMs
     s = api.default_config(1, 16, 28672, 8192)
-    assert (s.block_m, s.block_n, s.sched, s.cluster_m) == (16, 128, 2, 1) and s.stages == 12
+    assert (s.block_m, s.block_n, s.sched, s.cluster_m) == (16, 128, 2, 1)
+    assert s.stages == 9                                          # the shipped table's measured entry
+    assert api.heuristic_config(1, 16, 28672, 8192).stages == 0  # the heuristic leaves it to "as many as fit"
     assert api.default_config(1, 33, 28672, 8192).block_m == 64
     assert api.default_config(1, 16, 8192, 8192).sched == 0      # up to one wave of tiles: whole tiles
     # 65..128 rows keep 128-row tiles with a short A stage

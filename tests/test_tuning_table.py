@@ -44,15 +44,24 @@ def test_exact_shape_wins_and_replaces():
 
 def test_class_match_takes_the_nearest_entry_of_the_same_class():
     # class of 3000 is (12, 12, 12): 2049..4096
-    g.tuning_add(2304, 2304, 2304, g.GemmConfig(block_m=128, block_n=64, cluster_m=1, stages=3))
+    g.tuning_add(2304, 2304, 2304, g.GemmConfig(block_m=256, block_n=256, cluster_m=1, stages=3))
     g.tuning_add(4096, 4096, 4096, g.GemmConfig(block_m=128, block_n=192, cluster_m=1, stages=3))
     g.tuning_add(8192, 8192, 8192, g.GemmConfig(block_m=256, block_n=128, cluster_m=1, stages=3))
     assert tiles(g.default_config(1, 3800, 3800, 3800)) == (128, 192, 1)
-    assert tiles(g.default_config(1, 2500, 2500, 2500)) == (128, 64, 1)
+    assert tiles(g.default_config(1, 2500, 2500, 2500)) == (256, 256, 1)
     # another class: table silent, heuristic answers
     assert tiles(g.default_config(1, 1024, 1024, 1024)) == tiles(g.heuristic_config(1, 1024, 1024, 1024))
     # batched and plain problems never share entries
     assert tiles(g.default_config(4, 4096, 4096, 4096)) == tiles(g.heuristic_config(4, 4096, 4096, 4096))
+
+
+def test_a_neighbour_that_quantises_badly_on_this_shape_is_not_taken():
+    # 2048^3 measured best with 128 x 256 single-CTA tiles (128 tiles on 148 SMs). On 1536^3 the
+    # same tiles would be 72, on half the machine: the heuristic's own choice stands there.
+    g.tuning_add(2048, 2048, 2048, g.GemmConfig(block_m=128, block_n=256, cluster_m=1, stages=4))
+    assert tiles(g.default_config(1, 2048, 2048, 2048)) == (128, 256, 1)
+    assert tiles(g.default_config(1, 1536, 1536, 1536)) == tiles(g.heuristic_config(1, 1536, 1536, 1536))
+    assert tiles(g.default_config(1, 1920, 2048, 2048)) == (128, 256, 1)   # 120 tiles: still one full wave
 
 
 def test_stages_that_do_not_fit_a_neighbouring_shape_fall_back_to_as_many_as_fit():
@@ -77,16 +86,19 @@ def test_entries_without_a_kernel_are_refused():
 
 
 def test_load_file_roundtrip_and_errors(tmp_path):
-    assert g.tuning_load(MEASURED) == 4
-    assert g.tuning_size() == 4
+    n = len([l for l in MEASURED.read_text().splitlines() if l.split('#', 1)[0].strip()])
+    assert n >= 4 and g.tuning_load(MEASURED) == n
+    assert g.tuning_size() == n
     assert tiles(g.default_config(1, 2048, 2048, 2048)) == (128, 256, 1)
     assert g.default_config(1, 2048, 2048, 2048).stages == 4
     assert tiles(g.default_config(1, 8192, 8192, 8192)) == (256, 256, 2)
+    few = g.default_config(1, 16, 28672, 8192)
+    assert (few.block_m, few.sched, few.swap_ab, few.stages) == (16, 2, 1, 9)
     bad = tmp_path / "bad.table"
     bad.write_text("1 1024 1024 1024 128 128 1 4 0 0 0 0 0\n1 512 512 512 128 128 1\n")
     with pytest.raises(g.GemmError):
         g.tuning_load(bad)
-    assert g.tuning_size() == 4                      # nothing of a bad file is kept
+    assert g.tuning_size() == n                      # nothing of a bad file is kept
     nokernel = tmp_path / "nokernel.table"
     nokernel.write_text("1 1024 1024 1024 96 128 1 4 0 0 0 0 0\n")
     with pytest.raises(g.GemmError):
@@ -152,7 +164,7 @@ def test_environment_variable_loads_a_table_before_the_first_lookup():
             "print(g.tuning_size(), c.block_m, c.block_n, c.cluster_m, c.stages)")
     env = dict(os.environ, B200_GEMM_TUNING_TABLE=str(MEASURED))
     out = subprocess.run([sys.executable, "-c", code], cwd=REPO, env=env, capture_output=True, text=True, check=True)
-    assert out.stdout.split() == ["4", "128", "256", "1", "4"]
+    assert out.stdout.split()[1:] == ["128", "256", "1", "4"] and int(out.stdout.split()[0]) >= 4
 
 
 @pytest.mark.gpu
