@@ -283,7 +283,7 @@ def run_sweep(args):
     stream = torch.cuda.current_stream()
     for name, M, N, K, ka, kb in SWEEP_SHAPES:
         set_bytes = 2 * (M * K + N * K + M * N)
-        sets = max(1, min(64, -(-2 * 126_000_000 // set_bytes)))
+        sets = max(3 if M <= 128 else 1, min(64, -(-2 * 126_000_000 // set_bytes)))  # decode shapes: as the headline leg
         ops = []
         for i in range(sets):
             a, b = make_inputs(torch, M, N, K, ka, kb, seed=7 + i, device=device)

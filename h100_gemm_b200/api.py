@@ -122,6 +122,15 @@ def library() -> ctypes.CDLL:
         for f in (lib.b200_peer_alloc, lib.b200_peer_free, lib.b200_peer_export, lib.b200_peer_import,
                   lib.b200_peer_close):
             f.restype = ci
+    if hasattr(lib, "b200_mgemm_create"):
+        lib.b200_mgemm_create.argtypes = [ctypes.POINTER(vp), ci, ctypes.POINTER(ci), ci, ci, ci, ci]
+        lib.b200_mgemm_buffers.argtypes = [vp, ci, ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp)]
+        lib.b200_mgemm_run.argtypes = [vp]
+        lib.b200_mgemm_sync.argtypes = [vp, ctypes.POINTER(cf)]
+        lib.b200_mgemm_destroy.argtypes = [vp]
+        for f in (lib.b200_mgemm_create, lib.b200_mgemm_buffers, lib.b200_mgemm_run, lib.b200_mgemm_sync,
+                  lib.b200_mgemm_destroy):
+            f.restype = ci
     lib.b200_gemm_tuning_load.argtypes = [ctypes.c_char_p]
     lib.b200_gemm_tuning_load.restype = ci
     lib.b200_gemm_tuning_add.argtypes = [ci, ci, ci, ci, cfgp]
@@ -329,6 +338,63 @@ class DeviceBuffer:
             else:
                 library().b200_peer_free(self.ptr)
             self.ptr = None
+
+
+class MultiGemm:
+    """The single-process multi-GPU handle of the C ABI (b200_mgemm_*): rank p of `world` runs on
+    ``devices[p]`` and owns A [M_shard, K], B [N, K] and C ([M_shard, N], or with ``gather`` the full
+    [world * M_shard, N] that every rank's kernel writes into). Tensors returned by ``a``, ``b``
+    and ``c`` are views of the handle's device buffers."""
+
+    def __init__(self, world: int, M_shard: int, N: int, K: int, gather: bool = False, devices=None):
+        self.world, self.M, self.N, self.K, self.gather = world, M_shard, N, K, bool(gather)
+        self.devices = list(devices) if devices is not None else list(range(world))
+        self._h = ctypes.c_void_p()
+        arr = (ctypes.c_int * world)(*self.devices)
+        _check(library().b200_mgemm_create(ctypes.byref(self._h), world, arr, M_shard, N, K, int(self.gather)))
+
+    def _view(self, ptr: int, shape, device: int):
+        import torch
+        n = 1
+        for d in shape:
+            n *= d
+
+        class _Raw:
+            pass
+
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (n,), "typestr": "<i2", "data": (ptr, False), "version": 2}
+        with torch.cuda.device(device):
+            return torch.as_tensor(raw, device=f"cuda:{device}").view(torch.bfloat16).view(*shape)
+
+    def _buffers(self, rank: int):
+        a, b, c = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
+        _check(library().b200_mgemm_buffers(self._h, rank, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)))
+        return a.value, b.value, c.value
+
+    def a(self, rank: int):
+        return self._view(self._buffers(rank)[0], (self.M, self.K), self.devices[rank])
+
+    def b(self, rank: int):
+        return self._view(self._buffers(rank)[1], (self.N, self.K), self.devices[rank])
+
+    def c(self, rank: int):
+        rows = self.world * self.M if self.gather else self.M
+        return self._view(self._buffers(rank)[2], (rows, self.N), self.devices[rank])
+
+    def run(self) -> None:
+        _check(library().b200_mgemm_run(self._h))
+
+    def sync(self) -> float:
+        """Waits for every device; returns the slowest device's time for the last run in ms."""
+        ms = ctypes.c_float()
+        _check(library().b200_mgemm_sync(self._h, ctypes.byref(ms)))
+        return float(ms.value)
+
+    def close(self) -> None:
+        if self._h:
+            library().b200_mgemm_destroy(self._h)
+            self._h = ctypes.c_void_p()
 
 
 def gemm_gather(a, b, c_all_ptrs, rank: int, cfg: Optional[GemmConfig] = None, stream=None) -> None:

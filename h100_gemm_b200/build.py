@@ -93,7 +93,9 @@ def build_oracle() -> None:
     """The CPU checker used by tests and the benchmark's CPU leg (never by the library)."""
     oracle_dir = REPO_DIR / "oracle"
     _run(["make", "-C", str(oracle_dir), "all"])
-    reference = Path(os.environ.get("B200_REFERENCE_DIR", "/root/reference"))
+    # A checkout of the reference project: where B200_REFERENCE_DIR points, else a directory named
+    # "reference" beside this repository. Without one only the restatement is built.
+    reference = Path(os.environ.get("B200_REFERENCE_DIR") or REPO_DIR.parent / "reference")
     if (reference / "reference.h").exists():
         _run(["make", "-C", str(oracle_dir), "ref", f"REFERENCE={reference}"])
 

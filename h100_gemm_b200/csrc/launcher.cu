@@ -764,6 +764,14 @@ void build_sched(const Plan& p, const Problem& pr, int workers, SchedParams* s) 
   if (s->mode == kStreamK) units = sched_total_iters(*s);
   s->num_workers = static_cast<int>(units < workers ? units : workers);
   if (s->num_workers < 1) s->num_workers = 1;
+  if (s->mode == kDataParallel || s->mode == kSplitK) {
+    // Whole units in waves: with w waves needed anyway, ceil(units / w) workers finish at the same
+    // time as all of them would, and the SMs left idle return their share of the power budget to
+    // the ones that work (200 tiles on 74 CTA pairs are 3 waves; so are they on 67).
+    const long long waves = (units + s->num_workers - 1) / s->num_workers;
+    const long long needed = (units + waves - 1) / waves;
+    if (needed < s->num_workers) s->num_workers = static_cast<int>(needed);
+  }
 }
 
 WorkspaceLayout workspace_layout(const Plan& p, const Problem& pr, const SchedParams& s) {
@@ -1304,6 +1312,163 @@ int b200_peer_import(const unsigned char handle[64], void** ptr) {
 
 int b200_peer_close(void* ptr) {
   B200_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Several GPUs of one node driven from ONE process: the M-sharded GEMM behind a C handle
+// ------------------------------------------------------------------------------------------
+// The reference's second harness (matmul_h100_optimal.cu:115-229) is a single-process C++ main
+// around one launcher call; this is the same shape of interface for the row-sharded problem: rank
+// p of `world` holds M rows of A, all of B and either its own M rows of C (gather = 0, no exchange
+// at all) or a full copy of C that every rank's kernel writes into (gather = 1: the fused epilogue
+// of b200_gemm_bf16_gather over peer access, which one process gets from
+// cudaDeviceEnablePeerAccess without any IPC). One stream and one pair of events per device; the
+// time of a run is the maximum over the devices.
+struct b200_mgemm {
+  int world = 0, M = 0, N = 0, K = 0, gather = 0;
+  int device[kMaxGatherPeers] = {};
+  void* A[kMaxGatherPeers] = {};
+  void* B[kMaxGatherPeers] = {};
+  void* C[kMaxGatherPeers] = {};
+  void* ws[kMaxGatherPeers] = {};
+  size_t ws_bytes = 0;
+  cudaStream_t stream[kMaxGatherPeers] = {};
+  cudaEvent_t start[kMaxGatherPeers] = {}, stop[kMaxGatherPeers] = {};
+};
+
+namespace {
+struct DeviceRestore {
+  int saved = -1;
+  DeviceRestore() {
+    if (cudaGetDevice(&saved) != cudaSuccess) saved = -1;
+  }
+  ~DeviceRestore() {
+    if (saved >= 0) cudaSetDevice(saved);
+  }
+};
+}  // namespace
+
+int b200_mgemm_destroy(b200_mgemm* h) {
+  if (h == nullptr) return B200_OK;
+  DeviceRestore restore;
+  for (int p = 0; p < h->world; ++p) {
+    if (cudaSetDevice(h->device[p]) != cudaSuccess) continue;
+    if (h->stream[p]) cudaStreamSynchronize(h->stream[p]);
+    if (h->A[p]) cudaFree(h->A[p]);
+    if (h->B[p]) cudaFree(h->B[p]);
+    if (h->C[p]) cudaFree(h->C[p]);
+    if (h->ws[p]) cudaFree(h->ws[p]);
+    if (h->start[p]) cudaEventDestroy(h->start[p]);
+    if (h->stop[p]) cudaEventDestroy(h->stop[p]);
+    if (h->stream[p]) cudaStreamDestroy(h->stream[p]);
+  }
+  (void)cudaGetLastError();
+  delete h;
+  return B200_OK;
+}
+
+int b200_mgemm_create(b200_mgemm** out, int world, const int* devices, int M_shard, int N, int K, int gather) {
+  if (out == nullptr || world < 1 || world > kMaxGatherPeers || M_shard <= 0 || N <= 0 || K <= 0) {
+    return B200_ERR_INVALID_ARG;
+  }
+  if (gather != 0 && gather != 1) return B200_ERR_INVALID_ARG;
+  if (gather && N % 8 != 0) return B200_ERR_INVALID_ARG;
+  *out = nullptr;
+  DeviceRestore restore;
+  b200_mgemm* h = new b200_mgemm();
+  h->world = world;
+  h->M = M_shard;
+  h->N = N;
+  h->K = K;
+  h->gather = gather;
+  int rc = B200_OK;
+  auto fail = [&](int code) {
+    b200_mgemm_destroy(h);
+    return code;
+  };
+  h->ws_bytes = b200_gemm_workspace_bytes(1, M_shard, N, K, nullptr);
+  for (int p = 0; p < world; ++p) h->device[p] = devices ? devices[p] : p;
+  for (int p = 0; p < world && rc == B200_OK; ++p) {
+    if (cudaSetDevice(h->device[p]) != cudaSuccess) return fail(B200_ERR_CUDA);
+    const size_t c_bytes = static_cast<size_t>(gather ? world : 1) * M_shard * N * 2;
+    cudaError_t e = cudaMalloc(&h->A[p], static_cast<size_t>(M_shard) * K * 2);
+    if (e == cudaSuccess) e = cudaMalloc(&h->B[p], static_cast<size_t>(N) * K * 2);
+    if (e == cudaSuccess) e = cudaMalloc(&h->C[p], c_bytes);
+    if (e == cudaSuccess && h->ws_bytes > 0) e = cudaMalloc(&h->ws[p], h->ws_bytes);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream[p], cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreate(&h->start[p]);
+    if (e == cudaSuccess) e = cudaEventCreate(&h->stop[p]);
+    if (e != cudaSuccess) {
+      g_last_cuda_error = static_cast<int>(e);
+      (void)cudaGetLastError();
+      return fail(B200_ERR_CUDA);
+    }
+    // the fused gather stores into every other rank's copy of C: map them into this device
+    for (int q = 0; q < world && gather; ++q) {
+      if (h->device[q] == h->device[p]) continue;
+      int can = 0;
+      if (cudaDeviceCanAccessPeer(&can, h->device[p], h->device[q]) != cudaSuccess || !can) {
+        return fail(B200_ERR_UNSUPPORTED_CFG);
+      }
+      e = cudaDeviceEnablePeerAccess(h->device[q], 0);
+      if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+        g_last_cuda_error = static_cast<int>(e);
+        (void)cudaGetLastError();
+        return fail(B200_ERR_CUDA);
+      }
+      (void)cudaGetLastError();
+    }
+  }
+  *out = h;
+  return B200_OK;
+}
+
+int b200_mgemm_buffers(b200_mgemm* h, int rank, void** A, void** B, void** C) {
+  if (h == nullptr || rank < 0 || rank >= h->world) return B200_ERR_INVALID_ARG;
+  if (A) *A = h->A[rank];
+  if (B) *B = h->B[rank];
+  if (C) *C = h->C[rank];
+  return B200_OK;
+}
+
+int b200_mgemm_run(b200_mgemm* h) {
+  if (h == nullptr) return B200_ERR_INVALID_ARG;
+  DeviceRestore restore;
+  for (int p = 0; p < h->world; ++p) {
+    B200_CUDA_TRY(cudaSetDevice(h->device[p]));
+    B200_CUDA_TRY(cudaEventRecord(h->start[p], h->stream[p]));
+    int rc;
+    if (h->gather) {
+      rc = b200_gemm_bf16_gather(h->M, h->N, h->K, h->A[p], h->B[p], h->C, h->world, p, nullptr, h->stream[p]);
+    } else {
+      rc = run_gemm(1, h->M, h->N, h->K, h->A[p], 0, h->B[p], 0, h->C[p], 0, 1.0f, 0.0f, nullptr, h->ws[p],
+                    h->ws_bytes, h->stream[p]);
+    }
+    if (rc != B200_OK) return rc;
+    B200_CUDA_TRY(cudaEventRecord(h->stop[p], h->stream[p]));
+  }
+  return B200_OK;
+}
+
+int b200_mgemm_sync(b200_mgemm* h, float* ms_max) {
+  if (h == nullptr) return B200_ERR_INVALID_ARG;
+  DeviceRestore restore;
+  float worst = 0.0f;
+  for (int p = 0; p < h->world; ++p) {
+    B200_CUDA_TRY(cudaSetDevice(h->device[p]));
+    B200_CUDA_TRY(cudaStreamSynchronize(h->stream[p]));
+  }
+  for (int p = 0; p < h->world; ++p) {  // every device is done: with gather = 1 every copy of C is complete
+    float ms = 0.0f;
+    B200_CUDA_TRY(cudaSetDevice(h->device[p]));
+    if (cudaEventElapsedTime(&ms, h->start[p], h->stop[p]) == cudaSuccess) {
+      worst = ms > worst ? ms : worst;
+    } else {
+      (void)cudaGetLastError();  // no run yet
+    }
+  }
+  if (ms_max) *ms_max = worst;
   return B200_OK;
 }
 

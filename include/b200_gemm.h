@@ -224,6 +224,28 @@ int b200_peer_export(void* ptr, unsigned char handle[64]);
 int b200_peer_import(const unsigned char handle[64], void** ptr);
 int b200_peer_close(void* ptr);
 
+/* Several GPUs of one node from ONE process: the row-sharded GEMM behind a handle, for a C or C++
+ * harness in the style of the reference's second main (matmul_h100_optimal.cu:115-229: allocate,
+ * fill, launch in a loop, time). Rank p of `world` (<= 8) runs on devices[p] (NULL: device p) and
+ * owns device buffers A [M_shard, K], B [N, K] and C; the caller fills A and B (b200_mgemm_buffers
+ * hands the pointers out) and reads C.
+ *   gather = 0  C is [M_shard, N] per rank; the ranks exchange nothing.
+ *   gather = 1  C is the full [world * M_shard, N] on every rank, written by every rank's kernel
+ *               through peer access (the fused epilogue of b200_gemm_bf16_gather); needs N % 8 == 0
+ *               and peer access between the devices (B200_ERR_UNSUPPORTED_CFG otherwise).
+ * b200_mgemm_run enqueues one launch per device on the handle's own streams and returns;
+ * b200_mgemm_sync waits for all of them — after it, with gather = 1, every copy of C is complete —
+ * and reports the slowest device's time for the last run, from CUDA events on the launching
+ * streams. The current device is left as it was. A gather over NCCL instead of the fused epilogue is
+ * offered by the Python layer only (h100_gemm_b200/sharding.py), so that this library does not
+ * link a collective library. The reference has no multi-GPU path. */
+typedef struct b200_mgemm b200_mgemm;
+int b200_mgemm_create(b200_mgemm** handle, int world, const int* devices, int M_shard, int N, int K, int gather);
+int b200_mgemm_buffers(b200_mgemm* handle, int rank, void** A, void** B, void** C);
+int b200_mgemm_run(b200_mgemm* handle);
+int b200_mgemm_sync(b200_mgemm* handle, float* ms_max);
+int b200_mgemm_destroy(b200_mgemm* handle);
+
 /* Replaces reference_gpu_gemm(GemmParams) — reference.h:49-90: a plain SIMT GEMM (one thread per
  * 4x4 outputs, k ascending, fp32) used as an on-device cross-check for shapes too large for the
  * CPU oracle. */

@@ -292,6 +292,40 @@ def test_fused_gather_epilogue_on_one_device(g):
             buf.close()
 
 
+@pytest.mark.parametrize("gather", [False, True])
+def test_single_process_multi_gpu_handle(g, gather):
+    """b200_mgemm_*: the row-sharded GEMM from one process. With one device visible the ranks share
+    it (their kernels do not wait on one another); with more, rank p runs on device p. Every rank's
+    rows — and, with the fused gather, every rank's full copy — must equal the CPU oracle bit for
+    bit on integer-valued operands."""
+    import torch
+    from h100_gemm_b200 import api
+    world, M, N, K = 2, 512, 768, 328
+    ndev = torch.cuda.device_count()
+    devices = [p % ndev for p in range(world)]
+    b_bits = util.integer_bits((N, K), 31)
+    a_bits = [util.integer_bits((M, K), 32 + p) for p in range(world)]
+    want = np.concatenate([oracle.cpu_gemm(a, b_bits) for a in a_bits])
+    mg = api.MultiGemm(world, M, N, K, gather=gather, devices=devices)
+    try:
+        for p in range(world):
+            mg.a(p).copy_(util.to_device(a_bits[p]).to(f"cuda:{devices[p]}"))
+            mg.b(p).copy_(util.to_device(b_bits).to(f"cuda:{devices[p]}"))
+            mg.c(p).fill_(-3.0)
+        torch.cuda.synchronize()
+        for _ in range(2):
+            mg.run()
+            assert mg.sync() > 0.0
+        for p in range(world):
+            got = util.to_bits(mg.c(p))
+            assert np.array_equal(got, want if gather else want[p * M:(p + 1) * M]), f"rank {p}"
+    finally:
+        mg.close()
+    assert g.device_status()[0] == 0
+    with pytest.raises(api.GemmError):
+        api.MultiGemm(9, M, N, K)
+
+
 # ------------------------------------------------------------------------------------------------
 # Configuration 5: irregular shapes and the batched problem.
 # ------------------------------------------------------------------------------------------------

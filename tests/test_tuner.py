@@ -109,6 +109,10 @@ def test_comparison_harnesses_run():
     out = subprocess.run([str(bin_dir / "cublas_ref"), "1024", "512", "768", "5"], capture_output=True, text=True,
                          timeout=120)
     assert out.returncode == 0 and "CuBlas_TC" in out.stdout and "CuBlasLt" in out.stdout
+    # one process driving every visible GPU through b200_mgemm_* (a single device here or many)
+    out = subprocess.run([str(bin_dir / "matmul_b200_multi"), "1024", "768", "520", "3"], capture_output=True, text=True,
+                         timeout=300)
+    assert out.returncode == 0 and "Correct!" in out.stdout and "P=1" in out.stdout, out.stdout + out.stderr
 
 
 @pytest.mark.gpu
