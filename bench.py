@@ -302,6 +302,10 @@ def run_sweep(args):
             for k, fn in impls.items():
                 for i in range(3):
                     fn(*ops[i % sets])
+                if args.sweep_idle > 0:   # burst mode: every round starts from an idle, cool GPU
+                    torch.cuda.synchronize()
+                    time.sleep(args.sweep_idle)
+                    fn(*ops[0])
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(stream)
                 for i in range(iters):
@@ -335,6 +339,7 @@ def run_sweep(args):
             line["ours_tflops"] = flops / (ms["ours"] * 1e-3) / 1e12
             line["frac_of_bf16_burst_peak"] = line["ours_tflops"] / peaks["burst"]
         line["peaks"] = peaks["source"]
+        line["idle_before_each_round_s"] = args.sweep_idle
         print(json.dumps(line), flush=True)
         del ops, ws
         torch.cuda.empty_cache()
@@ -750,6 +755,9 @@ def main():
     ap.add_argument("--no-skinny", action="store_true", help="N = 1: skip the decode-shape (HBM-bound) leg")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for profiler captures)")
+    ap.add_argument("--sweep-idle", type=float, default=0.0,
+                    help="--sweep: seconds of idle before every timed round (bursts from a cool GPU instead of the "
+                         "sustained clock of a back-to-back sweep)")
     ap.add_argument("--sweep", action="store_true",
                     help="one GPU, kernel-only: this library beside cuBLAS and cuBLASLt over a list of shapes, "
                          "one JSON line per shape (not the headline line)")
