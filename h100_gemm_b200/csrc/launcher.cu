@@ -455,6 +455,22 @@ b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K, int sms = 0) {
       c.sched = kDataParallel;
     }
   }
+  // When whole tiles quantise badly (768 x 8192: 96 pair tiles on 74 CTA pairs are two waves, the
+  // second a third full), cutting the tiles x K-tiles space evenly over the workers wins although
+  // the partial tiles cost about 28 % (measured with 256 x 256 pair tiles: 768 x 8192 x 8192 88.8
+  // against 105 us, 256 x 28672 x 8192 102.9 against 105.7 us; 1024 x 8192 x 8192 loses, 113.8
+  // against 104.1 us, and the model says so).
+  {
+    const long long tiles = ((M + 255) / 256) * static_cast<long long>((N + 255) / 256) * batch;
+    const double workers = static_cast<double>(sms / 2);
+    const double cost = static_cast<double>(tiles) / workers * 128 * 256 * 1.05 * 1.28;
+    if (tiles > workers && cost < best) {
+      c.block_m = 128;
+      c.block_n = 256;
+      c.cluster_m = 2;
+      c.sched = kStreamK;
+    }
+  }
   return c;
 }
 
