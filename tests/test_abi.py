@@ -60,9 +60,12 @@ def test_workspace_sizes(lib):
     # split-K: split_k * tiles fp32 tiles
     cfg = C(block_n=128, cluster_m=1, sched=1, split_k=4)
     assert api.workspace_bytes(1, 128, 1024, 4096, cfg) == 4 * 8 * 128 * 128 * 4
-    # stream-K: one slot per worker plus 16 flag words each (148 SMs assumed without a device)
+    # stream-K: one slot per worker plus 16 flag words each. 148 SMs are assumed without a device;
+    # 224 tiles are streamed by 140 of them (8 tiles per 5 workers: few tiles are cut)
     cfg = C(block_n=128, cluster_m=1, sched=2)
-    assert api.workspace_bytes(1, 64, 28672, 8192, cfg) == 148 * 128 * 128 * 4 + 148 * 128
+    assert api.workspace_bytes(1, 64, 28672, 8192, cfg) == 140 * 128 * 128 * 4 + 140 * 128
+    # 37 tiles on 148 workers: every tile is cut in four, all workers are used
+    assert api.workspace_bytes(1, 64, 37 * 128, 8192, cfg) == 148 * 128 * 128 * 4 + 148 * 128
     # invalid sizes / unsupported configurations need nothing and report nothing
     assert api.workspace_bytes(1, 0, 10, 10, None) == 0
     assert api.workspace_bytes(1, 128, 128, 128, C(block_n=100)) == 0
@@ -83,7 +86,7 @@ def test_default_config(lib):
     t = api.default_config(1, 100, 28672, 8192)
     assert (t.block_m, t.sched, t.cluster_m) == (128, 2, 1)
     # few-rows stream-K workspace: one 128 x 16 fp32 slot and 16 flag words per SM
-    assert api.workspace_bytes(1, 16, 28672, 8192, None) == 148 * 128 * 16 * 4 + 148 * 128
+    assert api.workspace_bytes(1, 16, 28672, 8192, None) == 140 * 128 * 16 * 4 + 140 * 128
     with pytest.raises(api.GemmError):
         api.default_config(1, 0, 1, 1)
 
