@@ -463,12 +463,33 @@ b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K, int sms = 0) {
   {
     const long long tiles = ((M + 255) / 256) * static_cast<long long>((N + 255) / 256) * batch;
     const double workers = static_cast<double>(sms / 2);
-    const double cost = static_cast<double>(tiles) / workers * 128 * 256 * 1.05 * 1.28;
+    // (with several row tiles sharing a panel of B the even cut also costs their phase alignment in
+    // K — the panel is then read from HBM more than once — hence the larger factor)
+    const double cut_cost = (M + 255) / 256 == 1 ? 1.28 : 1.5;
+    const double cost = static_cast<double>(tiles) / workers * 128 * 256 * 1.05 * cut_cost;
     if (tiles > workers && cost < best) {
+      best = cost;
       c.block_m = 128;
       c.block_n = 256;
       c.cluster_m = 2;
       c.sched = kStreamK;
+    }
+    // Hybrid: the full waves as whole tiles, only the last, partly filled wave cut over all workers.
+    // The cut wave costs a fixed 15-20 us on top of its fill — 0.43 of a wave at K = 8192 (measured:
+    // 768 x 8192 x 8192, one full wave + 22 of 74 tiles, 80.7 against 93.1 us whole tiles and 89.9 us
+    // stream-K; 4096^3, three full + 34 of 74, loses 97.2 to 94.3) —, so it pays only when the last
+    // wave is less than a third full.
+    const long long w = static_cast<long long>(workers);
+    const long long full = tiles / w;
+    const double fill = static_cast<double>(tiles - full * w) / workers;
+    if (full >= 1 && fill > 0.0 && fill < 0.34) {
+      const double hybrid = (static_cast<double>(full) + fill + 0.43 * 8192.0 / (K < 512 ? 512 : K)) * 128 * 256 * 1.05;
+      if (hybrid < best) {
+        c.block_m = 128;
+        c.block_n = 256;
+        c.cluster_m = 2;
+        c.sched = kHybrid;
+      }
     }
   }
   return c;
