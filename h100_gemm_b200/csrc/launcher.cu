@@ -439,6 +439,15 @@ b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K, int sms = 0) {
     // Almost nothing is written (M rows): store straight from registers and give the staging
     // memory to the B ring instead (16+ stages in flight; measured best at 28672 x 8192).
     c.epilogue = 2;
+    // With nearly 128 real rows and no more 256-column tiles than SMs, one whole 128 x 256 tile per
+    // SM wins: no tile is cut, and every 16 KB of A staged serves 32 KB of B instead of 16
+    // (128 x 28672 x 8192, 112 tiles: 82.4 us in a burst and 88.7 us sustained against 83.8 / 89.5;
+    // at 96 rows it is level in a burst and 1.5 % slower sustained, so the bound is 96).
+    if (M > 96 && static_cast<long long>((N + 255) / 256) * batch <= sms) {
+      c.block_n = 256;
+      c.sched = kDataParallel;
+      c.epilogue = 1;
+    }
     return c;
   }
   double best = 0.0;

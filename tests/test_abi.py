@@ -83,8 +83,13 @@ def test_default_config(lib):
     assert api.default_config(1, 33, 28672, 8192).block_m == 64
     assert api.default_config(1, 16, 8192, 8192).sched == 0      # up to one wave of tiles: whole tiles
     # 65..128 rows keep 128-row tiles with a short A stage
-    t = api.default_config(1, 100, 28672, 8192)
-    assert (t.block_m, t.sched, t.cluster_m) == (128, 2, 1)
+    t = api.default_config(1, 90, 28672, 8192)
+    assert (t.block_m, t.block_n, t.sched, t.cluster_m) == (128, 128, 2, 1)
+    # nearly 128 rows and no more 256-column tiles than SMs: one whole 128 x 256 tile per SM
+    t = api.default_config(1, 128, 28672, 8192)
+    assert (t.block_m, t.block_n, t.sched, t.cluster_m) == (128, 256, 0, 1)
+    t = api.default_config(1, 128, 256 * 200, 8192)
+    assert (t.block_m, t.block_n, t.sched) == (128, 128, 2)
     # few-rows stream-K workspace: one 128 x 16 fp32 slot and 16 flag words per SM
     assert api.workspace_bytes(1, 16, 28672, 8192, None) == 140 * 128 * 16 * 4 + 140 * 128
     with pytest.raises(api.GemmError):
