@@ -396,10 +396,15 @@ double tile_cost(int block_m, int block_n, int cluster_m, int batch, int M, int 
 }
 
 int heuristic_sm_count() {
+  static std::atomic<int> cached[64];  // per device; 0 = not asked yet
   int dev = 0, v = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess &&
-      cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) {
-    return v;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+    v = cached[dev].load(std::memory_order_relaxed);
+    if (v > 0) return v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) {
+      cached[dev].store(v, std::memory_order_relaxed);
+      return v;
+    }
   }
   (void)cudaGetLastError();
   return 148;  // a full B200, when there is no device to ask (sizing a workspace on a build machine)
