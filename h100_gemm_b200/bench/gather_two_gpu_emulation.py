@@ -7,7 +7,10 @@ what the kernel and one link cost from what a switch and many writers into one m
         h100_gemm_b200/bench/gather_two_gpu_emulation.py [W=8]
 
 Prints one JSON line: ms per launch (CUDA events, max over the two ranks, 20 launches) for 256 and
-128 rows per CTA, and whether every region the peer wrote holds the peer's own result."""
+128 rows per CTA, and whether every region the peer wrote holds the peer's own result. With
+``--roles`` after W it adds, per tile shape, the cycle counters of one traced launch on rank 0
+(means over the CTAs): kernel total, MMA issuer waiting for operands, first epilogue warp waiting
+for an accumulator, and accumulator-ready to stores-issued."""
 import os, sys, json
 sys.path.insert(0, str(__import__("pathlib").Path(__file__).resolve().parents[2]))
 import torch, torch.distributed as dist
@@ -46,6 +49,23 @@ for rnd in range(2):
         t = torch.tensor([e0.elapsed_time(e1) / 20], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         out.setdefault(f"{tile} rows per CTA", []).append(round(float(t.item()), 4))
+roles = {}
+if "--roles" in sys.argv:
+    for tile, cfg in (("256", api.GemmConfig(block_m=256, block_n=256, cluster_m=2, epilogue=1)), ("128", api.GemmConfig(block_m=128, block_n=256, cluster_m=2, epilogue=1))):
+        counters = torch.zeros(148 * 8, dtype=torch.int64, device="cuda")
+        api.set_profile_buffer(counters)
+        try:
+            for _ in range(3):
+                api.gemm_gather(a, b, ptrs, rank, cfg=cfg, stream=stream); dist.all_reduce(token)
+            torch.cuda.synchronize(); dist.barrier()
+            counters.zero_()
+            api.gemm_gather(a, b, ptrs, rank, cfg=cfg, stream=stream); dist.all_reduce(token)
+            torch.cuda.synchronize()
+        finally:
+            api.set_profile_buffer(None)
+        mean = counters.view(148, 8).double().mean(0).tolist()
+        roles[f"{tile} rows per CTA"] = {name: int(mean[api.PROFILE_SLOTS.index(name)])
+                                        for name in ("total", "mma_wait_full", "epi_wait_full", "epi_busy")}
 # correctness of the last variant: what the PEER wrote into my buffer (regions q != peer's rank... it wrote to my_base + q*M*N*2 + peerrank*M*N elements)
 dist.barrier(); torch.cuda.synchronize()
 full = mine.tensor((16 * M, N))
@@ -60,7 +80,7 @@ for q in range(EMUL):
 own_ok = bool(torch.equal(full[rank * M:(rank + 1) * M].view(torch.int16), ref.view(torch.int16)))
 st = g.device_status()[0]
 if rank == 0:
-    print(json.dumps({"emulated_world": EMUL, "ms": out, "peer_regions_ok": ok, "own_ok": own_ok, "status": st}), flush=True)
+    print(json.dumps({"emulated_world": EMUL, "ms": out, "peer_regions_ok": ok, "own_ok": own_ok, "status": st, **({"cycles": roles} if roles else {})}), flush=True)
 dist.barrier()
 peer.close(); dist.barrier(); mine.close()
 dist.destroy_process_group()

@@ -161,6 +161,7 @@ struct KernelEntry {
   KernelFn fn_traced;  // same kernel with the cycle counters compiled in
   KernelFn fn_f16;     // same kernel for IEEE fp16 operands and output
   GatherFn fn_gather;  // same kernel storing every tile to up to 8 copies of C (256-column pair tiles only)
+  GatherFn fn_gather_traced;
   int b_bytes;    // bytes of B staged per CTA and K-tile
   int b_rows_cta;
   int block_m;    // rows of C per worker tile
@@ -168,10 +169,10 @@ struct KernelEntry {
   int epi_bytes;  // epilogue staging shared memory
 };
 
-template <int BN, int PAIR, int MT>
+template <int BN, int PAIR, int MT, int PROF>
 GatherFn gather_variant() {
   if constexpr (BN == 256 && PAIR == 1) {
-    return &gemm_kernel<BN, PAIR, MT, 0, 0, kMaxGatherPeers>;
+    return &gemm_kernel<BN, PAIR, MT, PROF, 0, kMaxGatherPeers>;
   } else {
     return nullptr;
   }
@@ -186,7 +187,8 @@ KernelEntry make_entry() {
                      &gemm_kernel<BN, PAIR, MT, 0, 0, 1>,
                      &gemm_kernel<BN, PAIR, MT, 1, 0, 1>,
                      &gemm_kernel<BN, PAIR, MT, 0, 1, 1>,
-                     gather_variant<BN, PAIR, MT>(),
+                     gather_variant<BN, PAIR, MT, 0>(),
+                     gather_variant<BN, PAIR, MT, 1>(),
                      T::kBBytes,
                      T::kBRowsCta,
                      T::kBlockM,
@@ -274,6 +276,7 @@ int max_resident_workers(DeviceState& st, const KernelEntry& e, int smem, int* o
   B200_CUDA_TRY(cudaFuncSetAttribute(e.fn_f16, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
   if (e.fn_gather != nullptr) {
     B200_CUDA_TRY(cudaFuncSetAttribute(e.fn_gather, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+    B200_CUDA_TRY(cudaFuncSetAttribute(e.fn_gather_traced, cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
   }
   if (smem > st.smem_optin) return B200_ERR_SMEM;
   int workers = st.sm_count;
@@ -1053,11 +1056,12 @@ int run_gemm(int batch, int M, int N, int K, const void* A, long long strideA, c
   attr[1].val.programmaticStreamSerializationAllowed = std::getenv("B200_GEMM_NO_PDL") ? 0 : 1;
   lc.attrs = attr;
   lc.numAttrs = 2;
-  // (the tracing build exists for bf16 only; fp16 and fused-gather launches are never traced)
-  if (f16 || gather_world > 0) args.profile = nullptr;
+  // (the tracing build exists for bf16 only; fp16 launches are never traced)
+  if (f16) args.profile = nullptr;
   args.gather_world = gather_world;
   if (gather_world > 0) {
-    B200_CUDA_TRY(cudaLaunchKernelEx(&lc, plan.kernel->fn_gather, map_a, map_b, gather_maps, args));
+    const GatherFn fn = args.profile ? plan.kernel->fn_gather_traced : plan.kernel->fn_gather;
+    B200_CUDA_TRY(cudaLaunchKernelEx(&lc, fn, map_a, map_b, gather_maps, args));
   } else {
     const KernelFn fn = f16 ? plan.kernel->fn_f16 : (args.profile ? plan.kernel->fn_traced : plan.kernel->fn);
     StoreMaps<1> one;
@@ -1346,8 +1350,9 @@ int b200_gemm_bf16_gather(int M, int N, int K, const void* A, const void* B, voi
     c.cluster_m = 2;
     c.block_n = 256;
     // 256 rows per CTA is the faster GEMM; from four ranks on the peer stores weigh more and the
-    // 128-row tile, whose epilogue overlaps the next main loop, measures faster (4 GPUs: 0.937 against
-    // 0.966 ms; 8 GPUs: 1.604 against 1.621 ms; 2 GPUs: 0.788 against 0.761 ms).
+    // 128-row tile, whose epilogue overlaps the next main loop and has half as many warps storing at
+    // once, measures faster (two GPUs carrying four ranks' traffic: 0.885 against 0.902 ms; eight ranks':
+    // 1.453 against 1.491 ms; two ranks: 0.782 against 0.746 ms).
     if (c.block_m != 256 || world >= 4) c.block_m = 128;
     c.sched = kDataParallel;
     c.epilogue = 1;
@@ -1589,10 +1594,8 @@ static int host_schedule(int M, int N, int K, const void* hA, const void* hB, vo
   if (dev < 0 || dev >= 64) return B200_ERR_INVALID_ARG;
   std::lock_guard<std::mutex> lock(g_host_mutex);
   HostPath& h = g_host[dev];
-  if (h.compute == nullptr) {
-    B200_CUDA_TRY(cudaStreamCreateWithFlags(&h.copy_in, cudaStreamNonBlocking));
-    B200_CUDA_TRY(cudaStreamCreateWithFlags(&h.compute, cudaStreamNonBlocking));
-    B200_CUDA_TRY(cudaStreamCreateWithFlags(&h.copy_out, cudaStreamNonBlocking));
+  for (cudaStream_t* s : {&h.copy_in, &h.compute, &h.copy_out}) {
+    if (*s == nullptr) B200_CUDA_TRY(cudaStreamCreateWithFlags(s, cudaStreamNonBlocking));
   }
 
   // Bands are multiples of 256 rows so every block tiles like a whole problem, and a block must be
@@ -1702,7 +1705,7 @@ void b200_gemm_host_release(void) {
   const bool have_device = cudaGetDevice(&current) == cudaSuccess;
   for (int dev = 0; dev < 64; ++dev) {
     HostPath& h = g_host[dev];
-    if (h.compute == nullptr && h.dA == nullptr && h.dB == nullptr && h.dC == nullptr && h.ws == nullptr) continue;
+    if (h.copy_in == nullptr && h.dA == nullptr && h.dB == nullptr && h.dC == nullptr && h.ws == nullptr) continue;
     if (cudaSetDevice(dev) != cudaSuccess) continue;
     if (h.dA) cudaFree(h.dA);
     if (h.dB) cudaFree(h.dB);

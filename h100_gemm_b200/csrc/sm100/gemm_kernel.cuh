@@ -222,6 +222,31 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
 // the kernel also performs the all-gather of a row-sharded C (every rank's copy of the full C,
 // this rank's own included, reached through peer-mapped device memory over NVLink).
 static constexpr int kMaxGatherPeers = 8;
+// Fused all-gather: every destination's store is a bulk group of its own, and the warp waits for
+// it to complete before it issues the next one. A store into a peer's memory completes when the
+// link has taken it, so a CTA never has more than one 4 KB block per epilogue warp in flight.
+// Without the limit the stores pile up behind the link inside the SM's path to memory and the
+// operand loads of the next tile queue behind them (measured with the cycle counters: at eight
+// ranks the MMA issuer waits for operands for 30 % of the kernel, against 4 % without peers).
+// Two GPUs carrying eight ranks' traffic: 1.507 -> 1.453 ms (128 rows per CTA), 1.515 -> 1.491 ms
+// (256); four ranks' traffic 0.923 -> 0.885 ms. Allowing one more group in flight gives it all back.
+B200_DEVICE void gather_store_issued() {
+  ptx::tma_store_commit();
+  ptx::tma_store_wait<0>();
+}
+
+// Before a warp refills a staging slab: the stores that read it last must have read it. With one
+// bulk group per block that is "all but the newest kSlabs - 1 groups"; with one group per
+// destination (NP > 1) the groups of one block are counted out by waiting for all of them.
+template <int NP, int kSlabs>
+B200_DEVICE void slab_reuse_wait() {
+  if constexpr (NP > 1) {
+    ptx::tma_store_wait_read<0>();
+  } else {
+    ptx::tma_store_wait_read<kSlabs - 1>();
+  }
+}
+
 template <int NP>
 struct StoreMaps {
   CUtensorMap m[NP];
@@ -653,7 +678,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           if (rows_live) {
             const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                     static_cast<uint32_t>(acc * T::kAccCols + mt * BN);
-            if (lane == 0) ptx::tma_store_wait_read<T::kSlabsPerWarp - 1>();  // the slab's last store has read it
+            if (lane == 0) slab_reuse_wait<NP, T::kSlabsPerWarp>();  // the slab's last store has read it
             __syncwarp();
             // 32 columns per read, two register buffers: the read of piece i + 1 is in flight while
             // piece i is converted. (Columns beyond N hold products of zero-filled rows of B: they
@@ -702,7 +727,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
               if (n0 < args.N) {
                 const uint32_t slab = slab0 + (store_count & (T::kSlabsPerWarp - 1)) * kEpiSlabBytes;
                 if (c > 0) {
-                  if (lane == 0) ptx::tma_store_wait_read<T::kSlabsPerWarp - 1>();
+                  if (lane == 0) slab_reuse_wait<NP, T::kSlabsPerWarp>();
                   __syncwarp();
 #pragma unroll
                   for (int h = 0; h < 2; ++h) {
@@ -720,11 +745,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                   if constexpr (NP > 1) {
                     for (int p = 0; p < args.gather_world; ++p) {
                       ptx::tma_store_3d(&maps_c.m[p], slab, n0, m_slab, tc.b);
+                      gather_store_issued();
                     }
                   } else {
                     ptx::tma_store_3d(&maps_c.m[0], slab, n0, m_slab, tc.b);
+                    ptx::tma_store_commit();
                   }
-                  ptx::tma_store_commit();
                 }
                 ++store_count;
               }
@@ -912,7 +938,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
         // bf16 -> swizzled staging slab -> TMA store of a 32-row x 64-column box.
         const uint32_t slab = slab0 + (store_count & (T::kSlabsPerWarp - 1)) * kEpiSlabBytes;
-        if (lane == 0) ptx::tma_store_wait_read<T::kSlabsPerWarp - 1>();  // the slab's last store has read it
+        if (lane == 0) slab_reuse_wait<NP, T::kSlabsPerWarp>();  // the slab's last store has read it
         __syncwarp();
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -931,13 +957,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         __syncwarp();
         if (lane == 0) {
           if constexpr (NP > 1) {
-            // fused all-gather: the same staged block goes to every rank's copy of C (one bulk
-            // group, so the slab is reused only after all of them have read it)
-            for (int p = 0; p < args.gather_world; ++p) ptx::tma_store_3d(&maps_c.m[p], slab, n0, m_slab, tc.b);
+            // fused all-gather: the same staged block goes to every rank's copy of C
+            for (int p = 0; p < args.gather_world; ++p) {
+              ptx::tma_store_3d(&maps_c.m[p], slab, n0, m_slab, tc.b);
+              gather_store_issued();
+            }
           } else {
             ptx::tma_store_3d(&maps_c.m[0], slab, n0, m_slab, tc.b);
+            ptx::tma_store_commit();
           }
-          ptx::tma_store_commit();
         }
         ++store_count;
       }

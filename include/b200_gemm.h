@@ -264,7 +264,7 @@ int b200_reference_gpu_gemm_f16(int M, int N, int K, const void* A, const void* 
 int b200_gemm_last_device_status(unsigned int out[4]);
 
 /* Optional tracing. While a device buffer of at least 8 * (number of CTAs) 64-bit words is
- * registered, every GEMM launch runs the tracing build of the kernel (a few percent slower) and
+ * registered, every bf16 launch (b200_gemm_bf16_gather included) runs the tracing build of the kernel (a few percent slower) and
  * writes eight cycle counters per CTA: [0] total, [1] producer wait, [2] MMA wait for operands,
  * [3] MMA wait for an accumulator buffer, [4] epilogue wait, [5] accumulator drain, [6] epilogue
  * busy, [7] tiles ([4]-[7] are those of the first epilogue warp). buffer == NULL switches it off. This is the working version of the debug

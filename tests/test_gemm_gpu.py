@@ -283,6 +283,18 @@ def test_fused_gather_epilogue_on_one_device(g):
         assert g.device_status()[0] == 0
         for v in views:
             assert np.array_equal(util.to_bits(v[(world - 1) * M:]), int_ref)
+        # the tracing build of the fused kernel: same bits, counters filled
+        prof = torch.zeros(148 * 8, dtype=torch.int64, device="cuda")
+        api.set_profile_buffer(prof)
+        try:
+            api.gemm_gather(shards[-1], util.to_device(int_b_bits), [buf.ptr for buf in bufs], world - 1)
+        finally:
+            api.set_profile_buffer(None)
+        assert g.device_status()[0] == 0
+        for v in views:
+            assert np.array_equal(util.to_bits(v[(world - 1) * M:]), int_ref)
+        counters = prof.view(148, 8).cpu().numpy()
+        assert counters[:, api.PROFILE_SLOTS.index("tiles")].sum() > 0 and (counters[:, 0] >= 0).all()
         # a tile shape the fused epilogue is not built for is refused, not mis-executed
         with pytest.raises(api.GemmError) as e:
             api.gemm_gather(shards[0], b, [buf.ptr for buf in bufs], 0, cfg=api.GemmConfig(block_n=128, cluster_m=1))
