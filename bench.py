@@ -343,6 +343,63 @@ def run_sweep(args):
         print(json.dumps(line), flush=True)
         del ops, ws
         torch.cuda.empty_cache()
+    batched_sweep_line(args, torch, g, device, stream, peaks)
+
+
+def batched_sweep_line(args, torch, g, device, stream, peaks, batch=32, M=2048, N=2048, K=512):
+    """The batched configuration (32 problems of 2048 x 2048 x 512): b200_gemm_batched_bf16 beside
+    torch.bmm (cuBLAS strided-batched underneath), two operand sets in rotation, interleaved rounds."""
+    import statistics
+    ops = []
+    for i in range(2):
+        a, b = make_inputs(torch, batch * M, batch * N, K, "uniform", "uniform", seed=31 + i, device=device)
+        ops.append((a.view(batch, M, K), b.view(batch, N, K),
+                    torch.empty(batch, M, N, dtype=torch.bfloat16, device=device)))
+    cfg = g.default_config(batch, M, N, K)
+    ws = torch.empty(max(g.workspace_bytes(batch, M, N, K, cfg), 1), dtype=torch.uint8, device=device)
+    impls = {
+        "ours": lambda a, b, c: g.gemm_batched(a, b, out=c, cfg=cfg, workspace=ws, stream=stream),
+        "torch_bmm": lambda a, b, c: torch.bmm(a, b.transpose(1, 2), out=c),
+    }
+    flops = 2.0 * batch * M * N * K
+    set_bytes = 2 * batch * (M * K + N * K + M * N)
+    rounds = {k: [] for k in impls}
+    for rnd in range(5):
+        for k, fn in impls.items():
+            for i in range(3):
+                fn(*ops[i % 2])
+            if args.sweep_idle > 0:
+                torch.cuda.synchronize()
+                time.sleep(args.sweep_idle)
+                fn(*ops[0])
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(100):
+                fn(*ops[i % 2])
+            e1.record(stream)
+            torch.cuda.synchronize()
+            rounds[k].append(e0.elapsed_time(e1) / 100)
+    rc, words = g.device_status()
+    if rc != 0:
+        raise SystemExit(f"device status {words}")
+    a, b, c = ops[0]
+    impls["ours"](a, b, c)
+    mine = c.float()
+    impls["torch_bmm"](a, b, c)
+    torch.cuda.synchronize()
+    scale = a.float().norm(dim=2).max() * b.float().norm(dim=2).max()
+    ms = {k: statistics.median(v) for k, v in rounds.items()}
+    tflops = flops / (ms["ours"] * 1e-3) / 1e12
+    print(json.dumps({
+        "shape": f"batched{batch}x{M}x{N}x{K}", "batch": batch, "M": M, "N": N, "K": K, "operand_sets": 2,
+        "iters_per_round": 100, "rounds": 5,
+        "config": {"block_m": cfg.block_m, "block_n": cfg.block_n, "cluster_m": cfg.cluster_m, "stages": cfg.stages,
+                   "sched": cfg.sched},
+        "ms": ms, "ours_over_torch_bmm_time": ms["ours"] / ms["torch_bmm"],
+        "max_err_vs_torch_bmm_norm_relative": float((mine - c.float()).abs().max() / scale),
+        "ours_tflops": tflops, "frac_of_bf16_burst_peak": tflops / peaks["burst"],
+        "ours_gbs": set_bytes / (ms["ours"] * 1e-3) / 1e9, "frac_of_hbm_peak": set_bytes / (ms["ours"] * 1e-3) / 1e9 / peaks["hbm_gbs"],
+        "peaks": peaks["source"], "idle_before_each_round_s": args.sweep_idle}), flush=True)
 
 
 def bind_to_gpu_numa_node(index: int):
