@@ -552,8 +552,34 @@ def run_ours(args):
     t = torch.tensor([ms_total], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_own = ms_total
     ms_total = float(t.item())
     ms_step = ms_total / args.steps
+
+    # ---- N > 1: every rank's own time, and rank 0 timed alone on the same shard ----
+    # (The N = 1 line runs configs[1] on U[-1,1] inputs, the N > 1 lines the prefill shard on normal
+    # inputs, which draw more power; `rank0_alone` is the one-GPU figure on THESE inputs, so the
+    # cost of running N GPUs at once can be read without mixing the two distributions.)
+    ranks = None
+    if world > 1:
+        every = [torch.zeros(1, dtype=torch.float64, device=device) for _ in range(world)]
+        dist.all_gather(every, torch.tensor([ms_own / args.steps], dtype=torch.float64, device=device))
+        alone_ms = None
+        if rank == 0:
+            time.sleep(0.5)
+            step(0)
+            torch.cuda.synchronize()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(stream)
+            for i in range(args.steps):
+                step(i)
+            a1.record(stream)
+            torch.cuda.synchronize()
+            alone_ms = a0.elapsed_time(a1) / args.steps
+        barrier()
+        ranks = {"ms_per_step_by_rank": [float(x.item()) for x in every], "rank0_alone_ms_per_step": alone_ms,
+                 "what": "rank0_alone: the same shard GEMM on rank 0 while the other GPUs idle (same inputs, `steps` "
+                         "launches after 0.5 s of idle)"}
 
     # ---- vendor baselines on the same buffers (reported next to the result, not a target) ----
     # Three interleaved rounds of (this library, cublasGemmEx, cublasLtMatmul), the order rotating from
@@ -785,6 +811,8 @@ def run_ours(args):
             line["sustained"] = sustained
         if skinny is not None:
             line["skinny"] = skinny
+        if ranks is not None:
+            line["ranks"] = ranks
         if gathered is not None:
             line["with_allgather"] = gathered
         if vendor is not None:
