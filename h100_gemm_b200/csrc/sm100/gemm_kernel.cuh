@@ -108,8 +108,8 @@ struct GemmArgs {
 
 template <int BN, int PAIR, int MT>
 struct KernelTraits {
-  static_assert(BN == 16 || BN == 32 || (BN % 64 == 0 && BN >= 64 && BN <= 256),
-                "BN must be 16, 32, 64, 128, 192 or 256");
+  static_assert(BN == 16 || BN == 32 || (BN % 64 == 0 && BN >= 64 && BN <= 256) || (BN == 224 && MT == 1),
+                "BN must be 16, 32, 64, 128, 192, 224 (whole tiles, one sub-tile) or 256");
   static_assert(MT == 1 || MT == 2, "one or two 128-row sub-tiles of A per CTA");
   static constexpr int kCtaGroup = PAIR ? 2 : 1;
   static constexpr int kUmmaM = kCtaRows * kCtaGroup;         // rows of one tcgen05.mma
@@ -135,7 +135,8 @@ struct KernelTraits {
                 "register split exceeds the CTA's launch allocation");
   static constexpr int kSlabsPerWarp = 2 / MT;                // TMA-store staging slabs per warp
   static constexpr int kEpiBytes = kEpiWarps * kSlabsPerWarp * kEpiSlabBytes;  // 32 KB
-  static constexpr int kAccCols = MT * BN;                    // TMEM columns of one accumulator buffer
+  // TMEM columns of one accumulator buffer (a 224-column tile gets 256: buffers start on 64-column steps)
+  static constexpr int kAccCols = MT * (BN < 64 ? BN : (BN + 63) / 64 * 64);
   static constexpr int kAccStages = (2 * kAccCols <= 512) ? 2 : 1;
   // One accumulator buffer of two sub-tiles: each sub-tile gets its own full/empty barrier pair, so
   // sub-tile 0 is read out while the tile's last MMAs still run on sub-tile 1, and the next tile's
@@ -496,7 +497,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // of that 128-row sub-tile, 64 columns at a time. The accumulator buffer is handed back to the
     // MMA issuer right after the warp's last TMEM read; conversion and stores of that last chunk
     // happen after the hand-back.
-    constexpr int kChunksPerSub = BN / kEpiChunkCols;
+    // (a 224-column tile ends in half a chunk: its last 32 columns are stored straight from registers)
+    constexpr int kChunksPerSub = (BN + kEpiChunkCols - 1) / kEpiChunkCols;
+    constexpr bool kHalfTail = BN >= kEpiChunkCols && BN % kEpiChunkCols != 0;
     const int e = warp - T::kEpiWarp0;
     const int q = warp & 3;
     const int mt = e >> 2;
@@ -851,6 +854,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
               v[h][j] = __float_as_uint(
                   __fadd_rn(__fmul_rn(__uint_as_float(v[h][j]), args.alpha), args.beta));
             }
+          }
+        }
+
+        if constexpr (kHalfTail) {
+          if (c == kChunksPerSub - 1) {
+            // The tile's last 32 columns (v[0]; v[1] lies beyond the tile): 64 bytes of this lane's row.
+            // Whole data-parallel tiles only — the launcher admits no other schedule for this width.
+            if (row_live) {
+              __nv_bfloat16* dst = args.C + tc.b * args.c_batch_stride +
+                                   static_cast<long long>(m_slab + static_cast<int>(lane)) * args.ldc + n0;
+              if (args.store_mode != kStoreScalar) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (n0 + 8 * j < args.N) {  // N is a multiple of 8 in these modes
+                    uint4 w;
+                    w.x = pack16<F16>(__uint_as_float(v[0][8 * j + 0]), __uint_as_float(v[0][8 * j + 1]));
+                    w.y = pack16<F16>(__uint_as_float(v[0][8 * j + 2]), __uint_as_float(v[0][8 * j + 3]));
+                    w.z = pack16<F16>(__uint_as_float(v[0][8 * j + 4]), __uint_as_float(v[0][8 * j + 5]));
+                    w.w = pack16<F16>(__uint_as_float(v[0][8 * j + 6]), __uint_as_float(v[0][8 * j + 7]));
+                    *reinterpret_cast<uint4*>(dst + 8 * j) = w;
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (n0 + j < args.N) {
+                    reinterpret_cast<uint16_t*>(dst)[j] =
+                        static_cast<uint16_t>(pack16<F16>(__uint_as_float(v[0][j]), 0.0f) & 0xFFFFu);
+                  }
+                }
+              }
+            }
+            continue;
           }
         }
 

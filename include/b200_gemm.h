@@ -40,7 +40,8 @@ typedef enum b200_status {
  *             shapes: a block_m x 128 tile computed with the operands swapped inside (128 rows of B
  *             on the MMA's M dimension, block_m rows of A on its N dimension) and stored
  *             transposed; see swap_ab below for its variants.
- *   block_n   columns of C per tile: 64, 128, 192 or 256.
+ *   block_n   columns of C per tile: 64, 128, 192 or 256; 224 with block_m = 128, cluster_m = 1 and
+ *             whole tiles (sched = 0) only.
  *   block_k   K-tile staged per pipeline stage: 64 (one 128-byte swizzle row).
  *   stages    shared-memory ring depth; 0 = as many as fit.
  *   cluster_m CTAs along M that share one B tile. 1 = single-CTA MMA. 2 = a CTA pair driving one

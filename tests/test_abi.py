@@ -85,9 +85,12 @@ def test_default_config(lib):
     # 65..128 rows keep 128-row tiles with a short A stage
     t = api.default_config(1, 90, 28672, 8192)
     assert (t.block_m, t.block_n, t.sched, t.cluster_m) == (128, 128, 2, 1)
-    # nearly 128 rows and no more 256-column tiles than SMs: one whole 128 x 256 tile per SM
+    # nearly 128 rows and no more 224-column tiles than SMs: one whole 128 x 224 tile per SM, stored from
+    # registers; 256-column tiles when only those fit one wave
     t = api.default_config(1, 128, 28672, 8192)
-    assert (t.block_m, t.block_n, t.sched, t.cluster_m) == (128, 256, 0, 1)
+    assert (t.block_m, t.block_n, t.sched, t.cluster_m, t.epilogue) == (128, 224, 0, 1, 2)
+    t = api.default_config(1, 128, 256 * 140, 8192)
+    assert (t.block_m, t.block_n, t.sched, t.cluster_m, t.epilogue) == (128, 256, 0, 1, 1)
     t = api.default_config(1, 128, 256 * 200, 8192)
     assert (t.block_m, t.block_n, t.sched) == (128, 128, 2)
     # few-rows stream-K workspace: one 128 x 16 fp32 slot and 16 flag words per SM

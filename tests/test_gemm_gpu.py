@@ -102,6 +102,38 @@ def test_golden_fixtures(g, path):
             assert_close(c, ref, a, b)
 
 
+@pytest.mark.parametrize("epilogue", [0, 1, 2])
+def test_224_column_tiles(g, config1, epilogue):
+    """The 128 x 224 tile (three 64-column chunks through the store path in use, the last 32 columns
+    from registers): configuration 1, every golden fixture (bf16 and fp16, alpha/beta), tails in M, N
+    and K with integer-valued inputs at three ring depths, and a batch."""
+    from h100_gemm_b200.api import GemmConfig as C
+    cfg = C(block_m=128, block_n=224, cluster_m=1, sched=0, epilogue=epilogue)
+    a, b, ref = config1
+    assert_close(run(g, a, b, cfg), ref, a, b)
+    for path in sorted(GOLDEN.glob("*.npz")):
+        if path.name == "config1_1024.npz":
+            continue
+        gold = np.load(path)
+        runner = run_f16 if path.name.startswith("f16_") else run
+        c = runner(g, gold["a"], gold["b"], cfg, float(gold["alpha"]), float(gold["beta"]))
+        if "integer" in path.stem:
+            assert np.array_equal(c, gold["c"]), path.stem
+        elif path.name.startswith("f16_"):
+            assert oracle.norm_relative_error(c, gold["c"], gold["a"], gold["b"], f16=True) <= TOL, path.stem
+        else:
+            assert_close(c, gold["c"], gold["a"], gold["b"])
+    for stages in (2, 3, 0):
+        ai, bi = util.integer_bits((300, 1544), 7), util.integer_bits((1352, 1544), 8)
+        cs = C(block_m=128, block_n=224, cluster_m=1, sched=0, epilogue=epilogue, stages=stages)
+        assert np.array_equal(run(g, ai, bi, cs), oracle.cpu_gemm(ai, bi))
+    ab, bb = util.integer_bits((3 * 200, 264), 9), util.integer_bits((3 * 456, 264), 10)
+    out = g.gemm_batched(util.to_device(ab).view(3, 200, 264), util.to_device(bb).view(3, 456, 264), cfg=cfg)
+    assert g.device_status()[0] == 0
+    for i in range(3):
+        assert np.array_equal(util.to_bits(out[i]), oracle.cpu_gemm(ab[i * 200:(i + 1) * 200], bb[i * 456:(i + 1) * 456]))
+
+
 @pytest.mark.parametrize("cfg", cfgs(), ids=cfg_id)
 @pytest.mark.parametrize("stages", [2, 3, 0])
 def test_integer_inputs_bit_exact(g, cfg, stages):
@@ -195,7 +227,7 @@ def test_skinny_decode(g, skinny_b, m):
     a = util.to_device(a_bits)
     ref = oracle.cpu_gemm(a_bits, b_bits)
     for cfg in (None, C(block_n=128, cluster_m=1, sched=1, split_k=4), C(block_n=64, cluster_m=1, sched=2),
-                C(block_n=256, cluster_m=1, sched=0)):
+                C(block_n=256, cluster_m=1, sched=0), C(block_n=224, cluster_m=1, sched=0, epilogue=1)):
         c = util.to_bits(g.gemm(a, b, cfg=cfg))
         assert g.device_status()[0] == 0
         assert_close(c, ref, a_bits, b_bits)
@@ -471,6 +503,11 @@ def test_error_codes(g):
     b = torch.zeros(256, 512, dtype=torch.bfloat16, device="cuda")
     for bad, status in ((C(block_n=100), api.STATUS_UNSUPPORTED_CFG), (C(block_m=48), api.STATUS_UNSUPPORTED_CFG),
                         (C(block_m=64, block_n=192), api.STATUS_UNSUPPORTED_CFG),
+                        # 224 columns: whole tiles of one CTA only
+                        (C(block_n=224, cluster_m=1, sched=2), api.STATUS_UNSUPPORTED_CFG),
+                        (C(block_n=224, cluster_m=2), api.STATUS_UNSUPPORTED_CFG),
+                        (C(block_m=256, block_n=224, cluster_m=1), api.STATUS_UNSUPPORTED_CFG),
+                        (C(block_n=224, cluster_m=1, epilogue=3), api.STATUS_UNSUPPORTED_CFG),
                         (C(block_m=128, block_n=512, swap_ab=1), api.STATUS_UNSUPPORTED_CFG),
                         (C(cluster_n=2), api.STATUS_UNSUPPORTED_CFG), (C(block_k=128), api.STATUS_UNSUPPORTED_CFG),
                         (C(block_n=256, cluster_m=1, stages=7), api.STATUS_SMEM), (C(sched=5), api.STATUS_INVALID_ARG)):

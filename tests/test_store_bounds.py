@@ -33,6 +33,14 @@ def _cases():
         ("vector-256x256", C(block_m=256, block_n=256, cluster_m=2, epilogue=2), (700, 776, 328)),
         ("staged-128x192", C(block_m=128, block_n=192, cluster_m=1, epilogue=3), tails),
         ("staged-256x256", C(block_m=256, block_n=256, cluster_m=2, epilogue=3), (700, 776, 328)),
+        # 224-column tiles end in half a chunk: three TMA boxes and 32 columns from registers.
+        # 520 = 224 + 224 + 72 (the last tile's half chunk lies beyond N), 424 = 224 + 192 + 8 (eight
+        # live columns in the half chunk), 517: 2-byte stores
+        ("tma-128x224", C(block_m=128, block_n=224, cluster_m=1, epilogue=1), tails),
+        ("tma-128x224-partial-half-chunk", C(block_m=128, block_n=224, cluster_m=1, epilogue=1), (300, 424, 264)),
+        ("vector-128x224", C(block_m=128, block_n=224, cluster_m=1, epilogue=2), (100, 1120, 264)),
+        ("scalar-odd-n-128x224", C(block_m=128, block_n=224, cluster_m=1), (300, 445, 264)),
+        ("default-128-rows-decode", None, (128, 2240, 520)),
         ("scalar-odd-n", C(block_m=128, block_n=128, cluster_m=1), odd_n),
         ("scalar-odd-n-256x256", C(block_m=256, block_n=256, cluster_m=2), (700, 773, 328)),
         ("few-rows-16", C(block_m=16, block_n=128, cluster_m=1), few),
