@@ -44,7 +44,7 @@ HBM_BOUND = {"skinny16", "skinny32", "skinny64", "skinny128"}
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one gemm_kernel launch, from ncu
 # captures of this benchmark's own command line on a B200; None where no capture exists.
 NCU_DRAM_BYTES_PER_LAUNCH = {"square8192": 9.414e8, "prefill_shard": 9.414e8, "skinny16": 4.773e8,
-                             "skinny64": 4.855e8, "skinny128": 4.982e8}
+                             "skinny64": 4.855e8, "skinny128": 4.752e8}
 INPUTS = {"uniform": "U[-1,1]", "normal": "N(0,1)", "normal0.02": "N(0,0.02)"}
 
 
