@@ -457,14 +457,20 @@ b200_gemm_cfg heuristic_cfg(int batch, int M, int N, int K, int sms = 0) {
     // 44 KB stages fit five deep without staging slabs (220 KB of loads in flight per SM against
     // 192 KB). Measured on two boxes, same process, interleaved: 82.9 against 84.6 us and 78.6
     // against 80.3 us in a burst, 87.5 / 90.2 and 82.2 / 83.7 us sustained.
-    if (M > 96 && static_cast<long long>((N + 255) / 256) * batch <= sms) {
+    // The 224-column tile also wins below 96 rows (80 x 28672 x 8192: 79.4 against 80.9 us stream-K
+    // in a burst, 83.7 / 85.5 sustained; 96 rows: 80.1 / 81.7 and 84.9 / 86.4).
+    // Whole tiles only while they keep more than half of the SMs busy: a narrow C with a long K is
+    // better cut along K.
+    const long long tiles224 = static_cast<long long>((N + 223) / 224) * batch;
+    const long long tiles256 = static_cast<long long>((N + 255) / 256) * batch;
+    if (M > 64 && tiles224 <= sms && 2 * tiles224 > sms) {
+      c.block_n = 224;
+      c.sched = kDataParallel;
+      c.epilogue = 2;
+    } else if (M > 96 && tiles256 <= sms && 2 * tiles256 > sms) {
       c.block_n = 256;
       c.sched = kDataParallel;
       c.epilogue = 1;
-      if (static_cast<long long>((N + 223) / 224) * batch <= sms) {
-        c.block_n = 224;
-        c.epilogue = 2;
-      }
     }
     return c;
   }

@@ -82,8 +82,11 @@ def test_default_config(lib):
     assert api.heuristic_config(1, 16, 28672, 8192).stages == 0  # the heuristic leaves it to "as many as fit"
     assert api.default_config(1, 33, 28672, 8192).block_m == 64
     assert api.default_config(1, 16, 8192, 8192).sched == 0      # up to one wave of tiles: whole tiles
-    # 65..128 rows keep 128-row tiles with a short A stage
+    # 65..128 rows keep 128-row tiles with a short A stage: whole 224-column tiles while they fit one
+    # wave, stream-K over 128-column tiles beyond
     t = api.default_config(1, 90, 28672, 8192)
+    assert (t.block_m, t.block_n, t.sched, t.cluster_m, t.epilogue) == (128, 224, 0, 1, 2)
+    t = api.default_config(1, 90, 256 * 200, 8192)
     assert (t.block_m, t.block_n, t.sched, t.cluster_m) == (128, 128, 2, 1)
     # nearly 128 rows and no more 224-column tiles than SMs: one whole 128 x 224 tile per SM, stored from
     # registers; 256-column tiles when only those fit one wave
