@@ -153,6 +153,14 @@ def test_heuristic_counts_waves_over_the_sms_it_is_given():
     assert api.heuristic_config_for_sms(1, 16, 128 * 140, 4096, 132).sched == 2
     # 4096^3: 128 pair tiles of 512 x 256 are two waves on 74 pairs; with 128 pairs they are one,
     # and so are the 256 tiles of 256 x 256 — the smaller tile then costs nothing extra
+    # 65..128 rows: whole 224-column tiles while they fit one wave of the device's SMs, 256-column
+    # ones (from 97 rows) when only those fit, stream-K beyond — and for a narrow C with a long K
+    h = api.heuristic_config_for_sms
+    assert (h(1, 128, 28672, 8192, 148).block_n, h(1, 128, 28672, 8192, 148).sched) == (224, 0)
+    assert (h(1, 128, 28672, 8192, 120).block_n, h(1, 128, 28672, 8192, 120).sched) == (256, 0)
+    assert (h(1, 128, 28672, 8192, 100).block_n, h(1, 128, 28672, 8192, 100).sched) == (128, 2)
+    assert (h(1, 80, 28672, 8192, 120).block_n, h(1, 80, 28672, 8192, 120).sched) == (128, 2)
+    assert (h(1, 128, 512, 65536, 148).block_n, h(1, 128, 512, 65536, 148).sched) == (128, 2)
     assert api.heuristic_config_for_sms(1, 4096, 4096, 4096, 148).block_m == 256
     assert api.heuristic_config_for_sms(1, 4096, 4096, 4096, 512).block_m == 128
     with pytest.raises(api.GemmError):
